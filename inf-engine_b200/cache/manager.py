@@ -34,6 +34,10 @@ class CacheRequirement:
     (values ``v_head_dim`` a head when that is given), all of them (``window`` None)
     or the last ``window``.
     With a window, ``keep_first`` keys at the start of the sequence stay as well (their pages are never given back).
+    ``chunk``: queries see only the keys of their own chunk of that many positions, so pages that lie wholly before
+    the chunk of the next token are given back.  ``n_v_heads``: heads of the value pool when it has fewer than the key
+    pool (several key heads share a value head).  ``values_in_keys``: the values are the first ``v_head_dim``
+    dimensions of the key rows, and no value pool is kept (the group's ``v`` is its ``k``).
     kind "state": one tensor of ``state_shape``/``state_dtype`` per request.
     kind "several": a run that keeps more than one thing (pages beside a state, two states): ``parts`` lists them,
     and the run's binding and view carry one entry per part, in that order.
@@ -50,15 +54,22 @@ class CacheRequirement:
     v_head_dim: int | None = None
     keep_first: int = 0
     parts: tuple = ()
+    chunk: int | None = None
+    n_v_heads: int | None = None
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim if self.v_head_dim is not None else self.head_dim
 
+    @property
+    def value_heads(self) -> int:
+        return self.n_v_heads if self.n_v_heads is not None else self.n_kv_heads
+
     def group_key(self):
         if self.kind == "kv":
             return ("kv", self.n_kv_heads, self.head_dim, self.value_dim, self.window, self.dtype,
-                    self.keep_first if self.window is not None else 0)
+                    self.keep_first if self.window is not None else 0, self.chunk, self.value_heads, self.values_in_keys)
         if self.kind == "state":
             return ("state", self.state_shape, self.state_dtype)
         return ("none",)
@@ -79,10 +90,17 @@ class KVGroup:
     v: torch.Tensor | None = None            # the same with v_head_dim as its last size
     v_head_dim: int = 0                      # 0: as head_dim
     keep_first: int = 0                      # with a window: this many first keys of a sequence stay
+    chunk: int | None = None                 # queries see their own chunk of this many positions only
+    n_v_heads: int = 0                       # 0: as n_kv_heads
+    values_in_keys: bool = False             # the values are the first dimensions of the key rows; ``v`` is ``k``
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def value_heads(self) -> int:
+        return self.n_v_heads or self.n_kv_heads
     tables: dict = field(default_factory=dict)      # request id -> list of page ids, -1 where released
     first_live: dict = field(default_factory=dict)  # request id -> first logical page still held
 
@@ -127,7 +145,9 @@ class CacheManager:
                     keys[key] = len(self.kv_groups)
                     self.kv_groups.append(KVGroup(len(self.kv_groups), req.n_kv_heads, req.head_dim, req.window,
                                                   req.dtype, [], PagePool(n_pages), v_head_dim=req.value_dim,
-                                                  keep_first=req.keep_first if req.window is not None else 0))
+                                                  keep_first=req.keep_first if req.window is not None else 0,
+                                                  chunk=req.chunk, n_v_heads=req.value_heads,
+                                                  values_in_keys=req.values_in_keys))
                 g = self.kv_groups[keys[key]]
                 g.entries.append(entry)
                 return CacheBinding("kv", g.index, len(g.entries) - 1)
@@ -163,15 +183,19 @@ class CacheManager:
             shape = (len(g.entries), self.n_pages, g.n_kv_heads, self.page_size)
             fill = float("nan") if self.poison_free_pages else 0.0
             g.k = torch.full(shape + (g.head_dim,), fill, dtype=g.dtype, device=self.device)
-            g.v = torch.full(shape + (g.value_dim,), fill, dtype=g.dtype, device=self.device)
+            if g.values_in_keys:
+                g.v = g.k
+            else:
+                g.v = torch.full((len(g.entries), self.n_pages, g.value_heads, self.page_size, g.value_dim), fill,
+                                 dtype=g.dtype, device=self.device)
         for g in self.state_groups:
             g.data = torch.zeros((len(g.entries), self.max_requests) + g.shape, dtype=g.dtype, device=self.device)
 
     def storage_bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += (len(g.entries) * self.n_pages * g.n_kv_heads * self.page_size * (g.head_dim + g.value_dim)
-                  * g.dtype.itemsize)
+            per_token = g.n_kv_heads * g.head_dim + (0 if g.values_in_keys else g.value_heads * g.value_dim)
+            n += len(g.entries) * self.n_pages * self.page_size * per_token * g.dtype.itemsize
         for g in self.state_groups:
             per = 1
             for s in g.shape:
@@ -200,9 +224,11 @@ class CacheManager:
 
     def _first_needed_page(self, g: KVGroup, length: int) -> int:
         """First logical page that a query at position >= ``length`` can still read."""
-        if g.window is None:
-            return 0
-        first_key = max(0, length - g.window + 1)
+        first_key = 0
+        if g.window is not None:
+            first_key = max(0, length - g.window + 1)
+        if g.chunk:
+            first_key = max(first_key, (length // g.chunk) * g.chunk)
         return first_key // self.page_size
 
     def pages_needed(self, rid, new_length: int) -> list[int]:
@@ -238,7 +264,7 @@ class CacheManager:
             raise PageAccountingError(f"request {rid!r} advanced to {new_length} beyond its reserved pages")
         self.lengths[rid] = new_length
         for g in self.kv_groups:
-            if g.window is None:
+            if g.window is None and not g.chunk:
                 continue
             first = self._first_needed_page(g, new_length)
             table = g.tables[rid]
@@ -255,7 +281,8 @@ class CacheManager:
         if self.poison_free_pages and pages and g.k is not None:
             idx = torch.tensor(pages, dtype=torch.long, device=g.k.device)
             g.k.index_fill_(1, idx, float("nan"))
-            g.v.index_fill_(1, idx, float("nan"))
+            if g.v is not g.k:
+                g.v.index_fill_(1, idx, float("nan"))
 
     def _any_table(self, rid):
         return self.kv_groups[0].tables[rid] if self.kv_groups else []

@@ -1,4 +1,5 @@
 from .barerax import BareraxConfig
+from .fovunex import FovunexConfig
 from .kipezen import KipezenConfig
 from .llama import ConfigError, LlamaConfig
 from .registry import (
@@ -14,6 +15,11 @@ from .registry import (
 )
 from .spec import (
     AttentionSpec,
+    DifferentialAttentionSpec,
+    LatentAttentionSpec,
+    MinGRUSpec,
+    ReinjectDecoderSpec,
+    YarnScaling,
     BigramDecoderSpec,
     BlockSpec,
     FeedForwardSpec,

@@ -114,3 +114,11 @@ def _kipezen(d: dict):
 
 
 register_architecture("Kipezen", _kipezen)
+
+
+def _fovunex(d: dict):
+    from .fovunex import FovunexConfig
+    return FovunexConfig.from_dict(d)
+
+
+register_architecture("Fovunex", _fovunex)

@@ -36,13 +36,28 @@ class NormSpec:
     weight: str        # tensor name of the gain
     bias: str | None = None   # tensor name of the additive term ("layernorm")
     unit_offset: bool = False  # "rmsnorm": the tensor is stored around zero and the multiplier is 1 + weight
+    scalar: bool = False       # "rmsnorm": the tensor is ONE number (shape ()), the multiplier of every coordinate
+
+
+@dataclass(frozen=True)
+class YarnScaling:
+    """Frequencies of a rotation blended for a context longer than the original one.  With ``dim(t) = dims *
+    ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(dim(fast)), 0)``, ``hi = min(ceil(dim(slow)), dims - 1)``
+    and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency of pair i is ``f_i / factor * ramp_i +
+    f_i * (1 - ramp_i)``, and cosine and sine are both multiplied by ``mult_slope * ln(factor) + 1``."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    mult_slope: float = 0.1
 
 
 @dataclass(frozen=True)
 class PositionSpec:
     """How positions enter a mixer."""
 
-    kind: str                     # "rotary" | "none" | "bucketed_bias" | "rotary_pairs"
+    kind: str                     # "rotary" | "none" | "bucketed_bias" | "rotary_pairs" | "rotary_partial"
     head_dim: int = 0
     theta: float = 0.0
     max_positions: int = 0
@@ -51,6 +66,11 @@ class PositionSpec:
     # position * theta^(-2i / rot_dims); the rest of the head passes unchanged.  Angles are worked out from the
     # position inside the kernel, so there is no table and no limit on positions.
     rot_dims: int = 0
+    # "rotary_partial": ``rot_dims`` dimensions of a head turn by position * theta^(-2i / rot_dims), paired in halves
+    # (i with i + rot_dims / 2) or as neighbours (2i with 2i + 1); where in the head they start is the mixer's
+    # business.  ``yarn`` blends the frequencies and multiplies cosine and sine.  No table, no limit on positions.
+    layout: str = "halves"        # "halves" | "neighbours"
+    yarn: YarnScaling | None = None
     # "bucketed_bias": a learned table [n_buckets, n_heads] added to the scores by distance; distances below half
     # the buckets have a row each, the rest share rows on a logarithmic scale that ends at ``max_distance``
     table: str = ""
@@ -110,6 +130,89 @@ class AttentionSpec(MixerSpec):
     @property
     def value_dim(self) -> int:
         return self.v_head_dim if self.v_head_dim is not None else self.head_dim
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Causal softmax attention whose keys and values are expanded from one compressed vector per token.
+
+    ``q_proj`` gives ``n_heads`` query heads laid out [head_dim unrotated, rot_dim rotated].  ``down_proj`` gives
+    ``kv_rank + rot_dim`` numbers a token: the first ``kv_rank``, RMS-normed with ``latent_norm`` (eps ``norm_eps``), are
+    the compressed vector c; the last ``rot_dim`` (not normed) are a rotated key part that all heads share.  Per head the
+    unrotated key is ``k_up`` c and the value ``v_up`` c (both laid out head by head); the score is (q_unrotated .
+    k_unrotated + q_rotated . k_rotated) * scale.  The cache holds c and the rotated key part only.  ``position``
+    (kind "rotary_partial" with rot_dims = rot_dim, or "none") turns the rotated parts.  ``chunk``: a query sees only
+    the keys of its own chunk of that many positions (None: every earlier key)."""
+
+    hidden: int = 0
+    n_heads: int = 0
+    head_dim: int = 0              # unrotated query/key dimensions of a head
+    rot_dim: int = 0               # rotated ones
+    v_head_dim: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    norm_eps: float = 1e-6
+    position: PositionSpec = PositionSpec(kind="none")
+    chunk: int | None = None
+    q_proj: str = ""
+    down_proj: str = ""
+    latent_norm: str = ""
+    k_up: str = ""
+    v_up: str = ""
+    o_proj: str = ""
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec(MixerSpec):
+    """Grouped-query attention with two score maps a head over the same values.
+
+    ``q_proj`` gives ``n_heads`` x 2 x ``head_dim`` and ``k_proj`` ``n_kv_heads`` x 2 x ``head_dim`` rows, laid out head by
+    head as [map 1, map 2]; ``v_proj`` ``n_kv_heads`` x ``v_head_dim``.  Every map of every head is RMS-normed over
+    ``head_dim`` with ``q_norm`` / ``k_norm`` (gains of that size, shared; eps ``norm_eps``; None: no norm), then
+    ``position`` turns its first dimensions.  Each map is a softmax attention of its own (score = q . k * scale,
+    causal, within a chunk of ``chunk`` positions when that is given).  With lambda = exp(sum(lq1 * lk1)) -
+    exp(sum(lq2 * lk2)) + lambda_init:  o = a1 - lambda a2, divided by its root mean square over the head's values
+    (``norm_eps``, no gain), times (1 - lambda_init), times sigmoid(``gate_proj`` x) if there is one, then
+    ``o_proj``."""
+
+    hidden: int = 0
+    n_heads: int = 0
+    n_kv_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    scale: float = 1.0
+    norm_eps: float = 1e-6
+    lambda_init: float = 0.0
+    position: PositionSpec = PositionSpec(kind="none")
+    chunk: int | None = None
+    q_proj: str = ""
+    k_proj: str = ""
+    v_proj: str = ""
+    q_norm: str | None = None
+    k_norm: str | None = None
+    lambda_q1: str = ""
+    lambda_k1: str = ""
+    lambda_q2: str = ""
+    lambda_k2: str = ""
+    gate_proj: str | None = None
+    o_proj: str = ""
+
+
+@dataclass(frozen=True)
+class MinGRUSpec(MixerSpec):
+    """A gated recurrence whose gates read the current token only, ``width`` channels:
+        z = sigmoid(z_proj x + z_bias);  u = x_proj x + x_bias;  candidate = u + 1/2 (u >= 0) | sigmoid(u) (u < 0)
+        S <- (1 - z) S + z candidate;   out = o_proj (S * silu(gate_proj x))
+    with S a float32 vector per request that starts at zero."""
+
+    hidden: int = 0
+    width: int = 0
+    z_proj: str = ""
+    z_bias: str = ""
+    x_proj: str = ""
+    x_bias: str = ""
+    gate_proj: str = ""
+    o_proj: str = ""
 
 
 @dataclass(frozen=True)
@@ -229,11 +332,15 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec(FeedForwardSpec):
-    """``down(act(gate(x)) * up(x))``."""
+    """``down(act(gate(x)) * (up(x) + up_offset))``.  ``activation`` "silu": g sigmoid(g).  "clamped_swish": with
+    g' = min(g, act_limit) and up clamped to [-act_limit, act_limit], g' sigmoid(act_alpha g')."""
 
     hidden: int = 0
     intermediate: int = 0
     activation: str = "silu"
+    act_alpha: float = 1.0
+    act_limit: float = 0.0
+    up_offset: float = 0.0
     gate_proj: str = ""
     up_proj: str = ""
     down_proj: str = ""
@@ -286,11 +393,17 @@ class BlockSpec:
     """One residual block: which norm, mixer and feed-forward, and how arranged.  A block without a feed-forward
     (``feedforward`` and ``ff_norm`` None) is its mixer half alone."""
 
-    kind: str                      # "prenorm": x += part(norm(x)) | "outnorm": x += norm(part(x))
+    kind: str       # "prenorm": x += part(norm(x)) | "outnorm": x += norm(part(x)) | "gated_prenorm" (below)
     mixer_norm: NormSpec
     mixer: MixerSpec
     ff_norm: NormSpec | None
     feedforward: FeedForwardSpec | None
+    # "gated_prenorm": x += sigmoid(W h + b) * part(h) with h = norm(x): a gate per coordinate that reads what the
+    # sublayer reads.  Tensor names of W ([hidden, hidden]) and b ([hidden]) for the mixer and the feed-forward.
+    mixer_gate: str | None = None
+    mixer_gate_bias: str | None = None
+    ff_gate: str | None = None
+    ff_gate_bias: str | None = None
 
 
 @dataclass(frozen=True)
@@ -334,3 +447,14 @@ class BigramDecoderSpec(ModelSpec):
     bigram_mul_prev: int = 0
     bigram_mul_cur: int = 0
     kind: str = "bigram_decoder"
+
+
+@dataclass(frozen=True)
+class ReinjectDecoderSpec(ModelSpec):
+    """A decoder whose token embedding is multiplied by ``embedding_scale`` and added to the residual stream again
+    right before each schedule entry that ``reinject_before`` names (a group of layers run several times in a row takes
+    the embedding anew at the start of every pass but the first)."""
+
+    embedding_scale: float = 1.0
+    reinject_before: tuple[int, ...] = ()
+    kind: str = "reinject_decoder"

@@ -17,7 +17,11 @@
 // (a learned temperature of each head), and values may have another head size
 // than queries and keys (hd_v; the pools are laid out with their own sizes).  Beside a window the first
 // `keep_first` keys of the sequence may stay visible to every later query, at their true positions, and the
-// output may take a multiplier (a mixer that is one of several summed side by side).
+// output may take a multiplier (a mixer that is one of several summed side by side).  With `chunk` a query at position
+// p sees keys from floor(p / chunk) * chunk on only (chunks are counted from the sequence's start, whatever the cut).
+// Several key heads may share one value head (`n_v_heads` less than the key heads: two score maps over the same
+// values), and the values may be the first dimensions of the key rows themselves (`v_row`: a compressed key/value
+// vector that is stored once).
 //
 // Work split: a block takes one (request, kv head) and a tile of 32
 // (token, head-in-group) pairs, so the `group` query heads that share a kv head
@@ -51,6 +55,10 @@ struct AttnGeneralParams {
   int hd_v;                 // head size of the values and of the output
   int keep_first;           // beside a window: keys at positions below this stay visible to every later query
   float out_scale;          // multiplier of the output
+  int chunk;                // > 0: a query sees only keys of its own chunk of this many positions (counted from position 0)
+  int n_v_heads;            // value heads in the value pool; kv head c reads value head c / (n_kv_heads / n_v_heads)
+  int v_row;                // elements between two value rows of the value pool (the value size, or a key row's size
+                            // when the values are the first dimensions of the keys and both pools are one)
 };
 
 template <typename T>
@@ -100,6 +108,8 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   const int my_t = row_valid ? my_pair / group : 0;
   const int my_limit = ctx + my_t;                                    // last visible key
   const int my_first = p.window > 0 ? max(0, my_limit - p.window + 1) : 0;
+  const int my_chunk0 = p.chunk > 0 ? (my_limit / p.chunk) * p.chunk : 0;
+  const int cv = c / (p.n_kv_heads / p.n_v_heads);
   const int my_head = c * group + (row_valid ? my_pair - my_t * group : 0);
   const float* my_bias = (p.score_bias != nullptr && row_valid) ? p.score_bias + (size_t)my_head * p.bias_dists : nullptr;
   const float my_scale = p.head_scale != nullptr ? p.scale * p.head_scale[my_head] : p.scale;
@@ -111,6 +121,11 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
     const int first_t = pair0 / group;
     key_begin = max(0, ctx + first_t - p.window + 1);
     key_begin = (key_begin / AG_KEYS) * AG_KEYS;
+  }
+  if (p.chunk > 0) {
+    // rows of a tile ascend in position: the first row's chunk starts first
+    const int c0 = ((ctx + pair0 / group) / p.chunk) * p.chunk;
+    key_begin = max(key_begin, (c0 / AG_KEYS) * AG_KEYS);
   }
   // with kept first keys the walk starts with their tiles and then jumps to the window's first tile
   const int keep = p.window > 0 ? p.keep_first : 0;
@@ -143,7 +158,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
       if (kp < key_end) {
         const int page = IE_PAGE(table[kp / p.page_size]);
         if (page >= 0)
-          vv = to_f32(vpool[(((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * hdv + d]);
+          vv = to_f32(vpool[(((size_t)page * p.n_v_heads + cv) * p.page_size + (kp % p.page_size)) * p.v_row + d]);
       }
       Vs[kk * hdv + d] = vv;
     }
@@ -160,7 +175,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
       const float* qr = Qs + row * ldq;
       const float* kr = Ks + kk * ldq;
       for (int d = 0; d < hd; ++d) dot += qr[d] * kr[d];
-      const bool visible = row_valid && kp <= my_limit && (kp >= my_first || kp < keep);
+      const bool visible = row_valid && kp <= my_limit && kp >= my_chunk0 && (kp >= my_first || kp < keep);
       float sc = dot * my_scale;
       if (visible && my_bias != nullptr) sc += my_bias[min(my_limit - kp, p.bias_dists - 1)];
       s[jj] = visible ? sc : -INFINITY;
@@ -218,13 +233,17 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
                                     int page_size, int window, float scale, int act_dtype, const float* score_bias,
                                     int bias_dists, const float* head_scale, int hd_v, int keep_first,
-                                    float out_scale, cudaStream_t stream) {
+                                    float out_scale, int chunk, int n_v_heads, int v_row, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if (hd_v <= 0) hd_v = hd;
   if (hd <= 0 || hd > 8 * AG_MAX_ACC || hd_v > 8 * AG_MAX_ACC) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads) return IE_BAD_SIZE;
   if (score_bias != nullptr && bias_dists <= 0) return IE_BAD_SIZE;
+  if (n_v_heads <= 0) n_v_heads = n_kv_heads;
+  if (v_row <= 0) v_row = hd_v;
+  if (n_kv_heads % n_v_heads || v_row < hd_v || chunk < 0 || (chunk > 0 && keep_first > 0)) return IE_BAD_SIZE;
   AttnGeneralParams p;
+  p.chunk = chunk; p.n_v_heads = n_v_heads; p.v_row = v_row;
   p.q = q; p.out = out; p.kpool = kpool; p.vpool = vpool; p.block_table = block_table;
   p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = work_req; p.work_pair0 = work_pair0;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
@@ -308,7 +327,9 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
   float* s_acc = s_dyn + ((hd + 3) & ~3);
   const int c = head / group;
   const int limit = p.ctx_before[r_id] + (n - q0);                       // last visible key
-  const int first = p.window > 0 ? max(0, limit - p.window + 1) : 0;
+  int first = p.window > 0 ? max(0, limit - p.window + 1) : 0;
+  if (p.chunk > 0) first = max(first, (limit / p.chunk) * p.chunk);
+  const int cv = c / (p.n_kv_heads / p.n_v_heads);
   const int n_keep = p.window > 0 ? min(p.keep_first, first) : 0;         // kept keys that the window does not hold anyway
   const int n_vis = n_keep + (limit - first + 1);
   const int* table = p.block_table + (size_t)r_id * p.table_stride;
@@ -327,12 +348,13 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
   for (int i0 = warp * 32; i0 < n_vis; i0 += AR_WARPS * 32) {
     const int idx = i0 + lane;
     float sc = -INFINITY;
-    long long at = -1;                             // this lane's key: its row in the pools
+    long long at = -1, vat_mine = -1;              // this lane's key: its row in the key pool and in the value pool
     if (idx < n_vis) {
       const int kp = idx < n_keep ? idx : first + (idx - n_keep);
       const int page = IE_PAGE(table[kp / p.page_size]);
       if (page >= 0) {
         at = ((long long)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size);
+        vat_mine = ((long long)page * p.n_v_heads + cv) * p.page_size + (kp % p.page_size);
         sc = key_dot(kpool + at * hd, qs, hd) * my_scale;
         if (my_bias != nullptr) sc += my_bias[min(limit - kp, p.bias_dists - 1)];
       }
@@ -353,10 +375,10 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
       for (int u = 0; u < VU; ++u) {
         const int kk = (kk0 + u) & 31;
         const float wk = __shfl_sync(0xffffffffu, e, kk);
-        const long long vat = __shfl_sync(0xffffffffu, at, kk);
+        const long long vat = __shfl_sync(0xffffffffu, vat_mine, kk);
         const bool live = kk0 + u < n_here && vat >= 0;
         w[u] = live ? wk : 0.f;
-        const T* vrow = vpool + (live ? vat : 0) * hdv;
+        const T* vrow = vpool + (live ? vat : 0) * p.v_row;
 #pragma unroll
         for (int j = 0; j < PL; ++j) {
           const int d = lane + 32 * j;
@@ -401,13 +423,17 @@ extern "C" int ie_attention_rows(const void* q, void* out, const void* kpool, co
                                  int n_tokens, int n_requests, int max_rows, int n_heads, int n_kv_heads, int hd,
                                  int page_size, int window, float scale, int act_dtype, const float* score_bias,
                                  int bias_dists, const float* head_scale, int hd_v, int keep_first, float out_scale,
-                                 cudaStream_t stream) {
+                                 int chunk, int n_v_heads, int v_row, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return IE_OK;
   if (hd_v <= 0) hd_v = hd;
   if (hd <= 0 || hd > 32 * AR_MAX_PER_LANE || hd_v > 32 * AR_MAX_PER_LANE) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_heads > 65535) return IE_BAD_SIZE;
   if (score_bias != nullptr && bias_dists <= 0) return IE_BAD_SIZE;
+  if (n_v_heads <= 0) n_v_heads = n_kv_heads;
+  if (v_row <= 0) v_row = hd_v;
+  if (n_kv_heads % n_v_heads || v_row < hd_v || chunk < 0 || (chunk > 0 && keep_first > 0)) return IE_BAD_SIZE;
   AttnGeneralParams p;
+  p.chunk = chunk; p.n_v_heads = n_v_heads; p.v_row = v_row;
   p.q = q; p.out = out; p.kpool = kpool; p.vpool = vpool; p.block_table = block_table;
   p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = nullptr; p.work_pair0 = nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;

@@ -1,0 +1,162 @@
+// Gates: element-by-element kernels of layers that gate what they add, and a gated recurrence without a hidden-state
+// input to its gates.  All arithmetic is float32 whatever the storage type.
+//
+// gated_residual_add:  residual += sigmoid(gate_pre + bias) * y          (residual float32; a gate per coordinate)
+// scale_rows:          x *= scale, and a copy of the result where asked   (a scaled embedding that is used again later)
+// glu_act:             out = act(g) * (u + up_offset) over rows that hold gate and up side by side or alternating:
+//                      kind 0: g * sigmoid(g);  kind 1: g' * sigmoid(alpha g') with g' = min(g, limit) and u clamped to
+//                      [-limit, limit]
+// mingru_scan:         z = sigmoid(z_pre + z_bias), u = u_pre + u_bias, candidate = u + 1/2 (u >= 0) | sigmoid(u) (u < 0)
+//                      S <- S + z (candidate - S)   [= (1 - z) S + z candidate],  out = S * silu(g_pre)
+//                      per channel, over each request's tokens of the step in order, from the float32 state of the
+//                      request's slot (negative slot: a padding row, skipped)
+#include "common.cuh"
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+template <typename T, typename TB>
+__global__ void gated_residual_add_kernel(float* __restrict__ residual, const T* __restrict__ y, int y_stride,
+                                          const T* __restrict__ gate, int gate_stride, const TB* __restrict__ bias,
+                                          int n_rows, int d) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_rows * d) return;
+  const int r = (int)(i / d), c = (int)(i - (size_t)r * d);
+  const float g = to_f32(gate[(size_t)r * gate_stride + c]) + (bias != nullptr ? to_f32(bias[c]) : 0.f);
+  residual[i] = fmaf(sigmoid_f(g), to_f32(y[(size_t)r * y_stride + c]), residual[i]);
+}
+
+extern "C" int ie_gated_residual_add(float* residual, const void* y, int y_stride, const void* gate, int gate_stride,
+                                     const void* bias, int bias_dtype, int n_rows, int d, int act_dtype,
+                                     cudaStream_t stream) {
+  const size_t n = (size_t)n_rows * d;
+  if (n == 0) return IE_OK;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+#define GR_GO(T, TB)                                                                                             \
+  return launch_k(gated_residual_add_kernel<T, TB>, blocks, 256, 0, stream, residual, (const T*)y, y_stride,     \
+                  (const T*)gate, gate_stride, (const TB*)bias, n_rows, d)
+  if (act_dtype == IE_F32 && bias_dtype == IE_F32) GR_GO(float, float);
+  if (act_dtype == IE_F32 && bias_dtype == IE_BF16) GR_GO(float, bf16);
+  if (act_dtype == IE_BF16 && bias_dtype == IE_F32) GR_GO(bf16, float);
+  if (act_dtype == IE_BF16 && bias_dtype == IE_BF16) GR_GO(bf16, bf16);
+#undef GR_GO
+  return IE_BAD_DTYPE;
+}
+
+__global__ void scale_rows_kernel(float* __restrict__ x, float* __restrict__ keep, float scale, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = x[i] * scale;
+  x[i] = v;
+  if (keep != nullptr) keep[i] = v;
+}
+
+extern "C" int ie_scale_rows(float* x, float* keep, float scale, int n_rows, int d, cudaStream_t stream) {
+  const size_t n = (size_t)n_rows * d;
+  if (n == 0) return IE_OK;
+  return launch_k(scale_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, keep, scale, n);
+}
+
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int in_stride, size_t total,
+                               int interleaved, int kind, float alpha, float limit, float up_offset) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int r = (int)(i / inter), j = (int)(i - (size_t)r * inter);
+  const T* row = in + (size_t)r * in_stride;
+  float g = to_f32(interleaved ? row[2 * j] : row[j]);
+  float u = to_f32(interleaved ? row[2 * j + 1] : row[inter + j]);
+  float a;
+  if (kind == 1) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    a = g * sigmoid_f(alpha * g);
+  } else {
+    a = g * sigmoid_f(g);
+  }
+  out[i] = from_f32<T>(a * (u + up_offset));
+}
+
+extern "C" int ie_glu_act(const void* in, void* out, int n_rows, int inter, int in_stride, int interleaved, int kind,
+                          float alpha, float limit, float up_offset, int act_dtype, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * inter;
+  if (total == 0) return IE_OK;
+  if (kind < 0 || kind > 1) return IE_BAD_SIZE;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (act_dtype == IE_F32)
+    return launch_k(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, inter, in_stride, total,
+                    interleaved, kind, alpha, limit, up_offset);
+  if (act_dtype == IE_BF16)
+    return launch_k(glu_act_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, inter, in_stride, total,
+                    interleaved, kind, alpha, limit, up_offset);
+  return IE_BAD_DTYPE;
+}
+
+#define MG_UNROLL 4
+
+template <typename T, typename TB>
+__global__ void mingru_scan_kernel(const T* __restrict__ z_pre, const T* __restrict__ u_pre, int zu_stride,
+                                   const T* __restrict__ g_pre, int g_stride, const TB* __restrict__ z_bias,
+                                   const TB* __restrict__ u_bias, float* __restrict__ state, T* __restrict__ out,
+                                   int out_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
+                                   int width, int write_state) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const int slot = IE_SLOT(slots[r]);
+  if (slot < 0) return;
+  const int t0 = q_start[r], t1 = q_start[r + 1];
+  const float bz = z_bias != nullptr ? to_f32(z_bias[c]) : 0.f, bu = u_bias != nullptr ? to_f32(u_bias[c]) : 0.f;
+  float S = state[(size_t)slot * width + c];
+  for (int t = t0; t < t1; t += MG_UNROLL) {
+    float zp[MG_UNROLL], up[MG_UNROLL], gp[MG_UNROLL];
+#pragma unroll
+    for (int i = 0; i < MG_UNROLL; ++i) {        // the loads of a few tokens on their way together: none depends on S
+      const bool live = t + i < t1;
+      const size_t row = (size_t)(live ? t + i : t);
+      zp[i] = to_f32(z_pre[row * zu_stride + c]);
+      up[i] = to_f32(u_pre[row * zu_stride + c]);
+      gp[i] = to_f32(g_pre[row * g_stride + c]);
+    }
+#pragma unroll
+    for (int i = 0; i < MG_UNROLL; ++i) {
+      if (t + i < t1) {
+        const float z = sigmoid_f(zp[i] + bz);
+        const float u = up[i] + bu;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        S = fmaf(z, cand - S, S);
+        out[(size_t)(t + i) * out_stride + c] = from_f32<T>(S * (gp[i] * sigmoid_f(gp[i])));
+      }
+    }
+  }
+  if (write_state) state[(size_t)slot * width + c] = S;
+}
+
+extern "C" int ie_mingru_scan(const void* z_pre, const void* u_pre, int zu_stride, const void* g_pre, int g_stride,
+                              const void* z_bias, const void* u_bias, int bias_dtype, float* state, void* out,
+                              int out_stride, const int* q_start, const int* slots, int n_requests, int width,
+                              int write_state, int act_dtype, cudaStream_t stream) {
+  if (n_requests <= 0 || width <= 0) return IE_OK;
+  if (n_requests > 65535) return IE_BAD_SIZE;
+  const int threads = 64;
+  dim3 grid((width + threads - 1) / threads, n_requests);
+#define MG_GO(T, TB)                                                                                              \
+  return launch_k(mingru_scan_kernel<T, TB>, grid, threads, 0, stream, (const T*)z_pre, (const T*)u_pre, zu_stride, \
+                  (const T*)g_pre, g_stride, (const TB*)z_bias, (const TB*)u_bias, state, (T*)out, out_stride,     \
+                  q_start, slots, width, write_state)
+  if (act_dtype == IE_F32 && bias_dtype == IE_F32) MG_GO(float, float);
+  if (act_dtype == IE_F32 && bias_dtype == IE_BF16) MG_GO(float, bf16);
+  if (act_dtype == IE_BF16 && bias_dtype == IE_F32) MG_GO(bf16, float);
+  if (act_dtype == IE_BF16 && bias_dtype == IE_BF16) MG_GO(bf16, bf16);
+#undef MG_GO
+  return IE_BAD_DTYPE;
+}
+
+IE_CHECK_API(gating)

@@ -80,7 +80,7 @@ def core():
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, I, P]
-        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, P]
+        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P]
         lib.ie_layernorm.argtypes = [P, P, P, P, I, P, I, P, I, I, F, P]
         lib.ie_embed_bigram.argtypes = [P, P, P, P, I, P, P, I, P, P, I, I, I, I, L, L, P]
         lib.ie_add_bias.argtypes = [P, I, P, I, I, I, I, P]
@@ -93,7 +93,7 @@ def core():
         lib.ie_cast_rows.argtypes = [P, P, I, I, I, P]
         lib.ie_outnorm_accumulate.argtypes = [P, P, I, I, P, I, P, I, I, I, F, P]
         lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, I, P]
-        lib.ie_attention_rows.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, P]
+        lib.ie_attention_rows.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P]
         lib.ie_linear_recurrence.argtypes = [P, I, P, I, P, P, I, P, P, P, I, P, P, I, P, P, I, I, F, F, I, I, P]
         lib.ie_rownorm_rotate_write.argtypes = [P, P, P, I, I, I, P, P, P, P, P, I, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_moe_route.argtypes = [P, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P]
@@ -101,6 +101,13 @@ def core():
         lib.ie_moe_gemm.argtypes = [P, I, P, I, P, I, P, P, I, I, I, I, I, L, I, I, I, I, P]
         lib.ie_moe_combine.argtypes = [P, P, P, P, I, I, P, I, I, I, P]
         lib.ie_moe_tile_rows.restype = c_int
+        lib.ie_head_prepare.argtypes = [P, I, I, I, I, I, P, P, I, I, I, I, I, P, I, P, I, I, I, F, P, I, I, F, P, P, P, P, I, I, I, P]
+        lib.ie_heads_gemm.argtypes = [P, I, I, I, P, I, P, I, I, I, I, I, I, I, P]
+        lib.ie_diff_combine.argtypes = [P, I, P, I, P, I, I, I, I, I, F, F, F, I, P]
+        lib.ie_gated_residual_add.argtypes = [P, P, I, P, I, P, I, I, I, I, P]
+        lib.ie_scale_rows.argtypes = [P, P, F, I, I, P]
+        lib.ie_glu_act.argtypes = [P, P, I, I, I, I, I, F, F, F, I, P]
+        lib.ie_mingru_scan.argtypes = [P, P, I, P, I, P, P, I, P, P, I, P, P, I, I, I, I, P]
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
         lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
         lib.ie_sample.argtypes = [P, P, P, I, I, L, P]
@@ -109,7 +116,9 @@ def core():
                      "ie_layernorm", "ie_embed_bigram", "ie_add_bias", "ie_tanh", "ie_polynorm",
                      "ie_headnorm_kv_write", "ie_gemm_simt_batched", "ie_cast_rows", "ie_outnorm_accumulate",
                      "ie_causal_conv", "ie_linear_recurrence", "ie_rownorm_rotate_write", "ie_moe_route", "ie_moe_sort",
-                     "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows", "ie_gemm_rowdot"):
+                     "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows", "ie_gemm_rowdot", "ie_head_prepare",
+                     "ie_heads_gemm", "ie_diff_combine", "ie_gated_residual_add", "ie_scale_rows", "ie_glu_act",
+                     "ie_mingru_scan"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -264,12 +273,15 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                       work_req: torch.Tensor, work_pair0: torch.Tensor, n_work: int, n_heads: int,
                       n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
                       score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
-                      v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0) -> None:
+                      v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0, chunk: int = 0,
+                      n_v_heads: int | None = None, v_row: int | None = None) -> None:
     """Paged causal attention in float32 arithmetic.  ``score_bias`` (float32 [n_heads, D], contiguous) is added to
     the scaled score of a query at position p and a key at position j as ``score_bias[head, min(p - j, D - 1)]``.
     ``head_scale`` (float32 [n_heads]) multiplies the score of its head beside ``scale``.  ``v_head_dim``: head size of
     the values and of ``out`` when it is not ``head_dim``.  ``keep_first``: beside a window, keys at positions below it
-    stay visible to every later query.  ``out_scale`` multiplies the output."""
+    stay visible to every later query.  ``out_scale`` multiplies the output.  ``chunk``: a query sees only the keys of
+    its own chunk of that many positions.  ``n_v_heads``: heads of the value pool when several key heads share a value
+    head; ``v_row``: elements between value rows when the values are the first dimensions of the key rows (one pool)."""
     assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     if score_bias is not None:
@@ -282,7 +294,8 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                                        n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
                                        dtype_code(q.dtype), _ptr(score_bias),
                                        score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
-                                       int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale), _stream()),
+                                       int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale),
+                                       int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
            f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -290,7 +303,8 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpoo
                    q_start: torch.Tensor, ctx_before: torch.Tensor, n_requests: int, max_rows: int, n_heads: int,
                    n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
                    score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
-                   v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0) -> None:
+                   v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0, chunk: int = 0,
+                   n_v_heads: int | None = None, v_row: int | None = None) -> None:
     """``attention_general`` for the requests of the step that bring at most ``max_rows`` (token, head-in-group) rows
     (decode tokens, as a rule): a block per (token, query head) whose warps split the visible keys.  Rows of requests
     that bring more are left untouched (the tile kernel's, with a work list of those requests)."""
@@ -305,7 +319,8 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpoo
                                     n_requests, int(max_rows), n_heads, n_kv_heads, head_dim, page_size, int(window or 0),
                                     float(scale), dtype_code(q.dtype), _ptr(score_bias),
                                     score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
-                                    int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale), _stream()),
+                                    int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale),
+                                    int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
            f"attention_rows(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -429,6 +444,116 @@ def rownorm_rotate_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_bi
                                           int(rot_dims), _ptr(positions), _ptr(slot_mapping), _ptr(kpool), _ptr(vpool), n,
                                           n_heads, n_kv_heads, head_dim, v_head_dim, page_size, dtype_code(q.dtype),
                                           _stream()), "rownorm_rotate_write")
+
+
+# ------------------------------------------------------------------ heads before and after attention, gates
+def head_prepare(q: torch.Tensor, q_heads: int, q_head_dim: int, k: torch.Tensor, k_heads: int, k_head_dim: int,
+                 positions: torch.Tensor, slot_mapping: torch.Tensor | None, kpool: torch.Tensor | None, page_size: int,
+                 q_gain: torch.Tensor | None = None, q_norm_dims: int = 0, k_gain: torch.Tensor | None = None,
+                 k_norm_dims: int = 0, eps: float = 0.0, inv_freq: torch.Tensor | None = None, rot_dims: int = 0,
+                 q_rot_off: int = 0, k_rot_off: int = 0, neighbours: bool = False, mult: float = 1.0,
+                 v: torch.Tensor | None = None, vpool: torch.Tensor | None = None, n_v_heads: int = 0,
+                 v_head_dim: int = 0) -> None:
+    """Per token: an RMS norm over the first ``*_norm_dims`` dimensions of every query head and key head (gains of that
+    size; None: no norm), a rotation by position of ``rot_dims`` dimensions that start at ``*_rot_off`` of every head
+    (``inv_freq`` float64 [rot_dims / 2]; in halves, or in neighbouring pairs with ``neighbours``; sine and cosine times
+    ``mult``); q is written back in place, the keys go to their slots of ``kpool`` [pages, k_heads, page_size,
+    k_head_dim] and ``v`` (optional, as it is) to ``vpool`` [pages, n_v_heads, page_size, v_head_dim]."""
+    n = q.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and q.dtype == k.dtype and (v is None or (v.stride(1) == 1 and v.dtype == q.dtype))
+    gains = [g for g in (q_gain, k_gain) if g is not None]
+    assert all(g.dtype == gains[0].dtype and g.is_contiguous() for g in gains)
+    assert q_gain is None or q_gain.numel() >= q_norm_dims
+    assert k_gain is None or k_gain.numel() >= k_norm_dims
+    assert inv_freq is None or (inv_freq.dtype is torch.float64 and inv_freq.is_contiguous() and inv_freq.numel() * 2 >= rot_dims)
+    assert kpool is None or kpool.dtype == q.dtype
+    _check(core().ie_head_prepare(_ptr(q), q.stride(0), q_heads, q_head_dim, int(q_norm_dims if q_gain is not None else 0),
+                                  int(q_rot_off), _ptr(q_gain), _ptr(k), k.stride(0), k_heads, k_head_dim,
+                                  int(k_norm_dims if k_gain is not None else 0), int(k_rot_off), _ptr(k_gain),
+                                  dtype_code(gains[0].dtype) if gains else IE_F32, _ptr(v),
+                                  v.stride(0) if v is not None else 0, int(n_v_heads), int(v_head_dim), float(eps),
+                                  _ptr(inv_freq), int(rot_dims if inv_freq is not None else 0), 1 if neighbours else 0,
+                                  float(mult), _ptr(positions), _ptr(slot_mapping), _ptr(kpool), _ptr(vpool), n,
+                                  page_size, dtype_code(q.dtype), _stream()), "head_prepare")
+
+
+def heads_gemm(x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor, o_head: int) -> None:
+    """A product per head in float32 arithmetic: ``out[m, h * o_head + j] = sum_k x[m, h * x_head + k] * w[h, k, j]`` for
+    ``w`` [heads, K, N] (contiguous); ``x`` and ``out`` are rows with a stride, a head every ``x_head`` / ``o_head``
+    elements."""
+    H, K, N = w.shape
+    m = x.shape[0]
+    assert w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == m
+    assert (H - 1) * x_head + K <= x.shape[1] and (H - 1) * o_head + N <= out.shape[1]
+    _check(core().ie_heads_gemm(_ptr(x), dtype_code(x.dtype), x.stride(0), int(x_head), _ptr(w), dtype_code(w.dtype),
+                                _ptr(out), dtype_code(out.dtype), out.stride(0), int(o_head), m, H, K, N, _stream()),
+           f"heads_gemm({x.dtype},{w.dtype}->{out.dtype}, heads={H}, k={K}, n={N})")
+
+
+def diff_combine(maps: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                 v_head_dim: int, lam: float, eps: float, out_mult: float) -> None:
+    """Two attention maps of every head become one output: ``o = a1 - lam * a2``, divided by its root mean square over
+    the head (``eps`` inside the root), times ``out_mult`` and, if given, ``sigmoid(gate)``.  ``maps`` is [n, kv heads,
+    2, heads of a group, v_head_dim] flattened; ``gate`` and ``out`` are [n, n_heads * v_head_dim]."""
+    n = out.shape[0]
+    assert maps.stride(1) == 1 and out.stride(1) == 1 and maps.dtype == out.dtype
+    assert maps.shape[1] == 2 * n_heads * v_head_dim and out.shape[1] == n_heads * v_head_dim
+    assert gate is None or (gate.stride(1) == 1 and gate.dtype == out.dtype and gate.shape == out.shape)
+    _check(core().ie_diff_combine(_ptr(maps), maps.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                  _ptr(out), out.stride(0), n, n_heads, n_kv_heads, v_head_dim, float(lam), float(eps),
+                                  float(out_mult), dtype_code(out.dtype), _stream()), "diff_combine")
+
+
+def gated_residual_add(residual: torch.Tensor, y: torch.Tensor, gate_pre: torch.Tensor, bias: torch.Tensor | None) -> None:
+    """residual (float32) += sigmoid(gate_pre + bias) * y, element by element; ``bias`` [d] or None."""
+    n, d = residual.shape
+    assert residual.dtype is torch.float32 and residual.is_contiguous()
+    assert y.shape == (n, d) and gate_pre.shape == (n, d) and y.stride(1) == 1 and gate_pre.stride(1) == 1
+    assert y.dtype == gate_pre.dtype and (bias is None or (bias.shape == (d,) and bias.is_contiguous()))
+    _check(core().ie_gated_residual_add(_ptr(residual), _ptr(y), y.stride(0), _ptr(gate_pre), gate_pre.stride(0),
+                                        _ptr(bias), dtype_code(bias.dtype) if bias is not None else IE_F32, n, d,
+                                        dtype_code(y.dtype), _stream()), "gated_residual_add")
+
+
+def scale_rows(x: torch.Tensor, scale: float, keep: torch.Tensor | None = None) -> None:
+    """x (float32) *= scale; ``keep`` (float32, same shape) takes a copy of the result."""
+    assert x.dtype is torch.float32 and x.is_contiguous()
+    assert keep is None or (keep.dtype is torch.float32 and keep.is_contiguous() and keep.shape == x.shape)
+    _check(core().ie_scale_rows(_ptr(x), _ptr(keep), float(scale), x.shape[0], x.shape[1], _stream()), "scale_rows")
+
+
+GLU_KINDS = {"silu": 0, "clamped_swish": 1}
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, kind: str, interleaved: bool = False, alpha: float = 1.0,
+            limit: float = 0.0, up_offset: float = 0.0) -> None:
+    """out[n, j] = act(gate_j) * (up_j + up_offset).  ``silu``: g sigmoid(g).  ``clamped_swish``: g' sigmoid(alpha g')
+    with g' = min(g, limit), and up clamped to [-limit, limit].  Gate and up are the two halves of a row, or alternate
+    when ``interleaved``."""
+    n, inter = out.shape
+    assert gate_up.shape == (n, 2 * inter) and gate_up.stride(1) == 1 and out.is_contiguous() and gate_up.dtype == out.dtype
+    _check(core().ie_glu_act(_ptr(gate_up), _ptr(out), n, inter, gate_up.stride(0), 1 if interleaved else 0,
+                             GLU_KINDS[kind], float(alpha), float(limit), float(up_offset), dtype_code(out.dtype),
+                             _stream()), f"glu_act({kind})")
+
+
+def mingru_scan(z_pre: torch.Tensor, u_pre: torch.Tensor, g_pre: torch.Tensor, z_bias: torch.Tensor | None,
+                u_bias: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                slots: torch.Tensor, n_requests: int, write_state: bool = True) -> None:
+    """The minGRU over each request's tokens of the step, per channel: z = sigmoid(z_pre + z_bias), u = u_pre + u_bias,
+    candidate = u + 1/2 where u >= 0 and sigmoid(u) where u < 0, S <- (1 - z) S + z candidate, out = S * silu(g_pre).
+    ``z_pre`` and ``u_pre`` are columns of one buffer (one row stride); ``state`` float32 [slots, width]."""
+    n, width = out.shape
+    assert z_pre.shape == u_pre.shape == g_pre.shape == (n, width) and z_pre.stride(0) == u_pre.stride(0)
+    assert z_pre.stride(1) == 1 and u_pre.stride(1) == 1 and g_pre.stride(1) == 1 and out.stride(1) == 1
+    assert z_pre.dtype == u_pre.dtype == g_pre.dtype == out.dtype
+    assert state.dtype is torch.float32 and state.is_contiguous() and state.shape[1:] == (width,)
+    biases = [b for b in (z_bias, u_bias) if b is not None]
+    assert all(b.dtype == biases[0].dtype and b.shape == (width,) and b.is_contiguous() for b in biases)
+    _check(core().ie_mingru_scan(_ptr(z_pre), _ptr(u_pre), z_pre.stride(0), _ptr(g_pre), g_pre.stride(0), _ptr(z_bias),
+                                 _ptr(u_bias), dtype_code(biases[0].dtype) if biases else IE_F32, _ptr(state), _ptr(out),
+                                 out.stride(0), _ptr(q_start), _ptr(slots), n_requests, width, 1 if write_state else 0,
+                                 dtype_code(out.dtype), _stream()), f"mingru_scan(width={width})")
 
 
 # ------------------------------------------------------------------ a mixture of experts
@@ -959,7 +1084,7 @@ def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, wo
 # (the device has no sanitizer here: this is what stands in for one while debugging a cache manager or a new part)
 CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "delta_rule", "gated_delta")
 CHECK_UNITS = ("elementwise", "rowwise", "sequence", "attention_general", "attention_mma", "attention_tcgen05",
-               "delta_rule", "gated_delta")
+               "delta_rule", "gated_delta", "headwise", "gating")
 CHECK_CODES = {1: "page id", 2: "cache slot", 3: "token id"}
 _check_limits: tuple[int, int, int] | None = None
 

@@ -1,14 +1,15 @@
-from . import attention, block, delta_rule, feedforward, gated_delta, model, norms, positions, recurrence, routed  # noqa: F401  (register the built-in parts)
+from . import attention, block, delta_rule, feedforward, gated_delta, latent, model, norms, positions, recurrence, routed  # noqa: F401  (register the built-in parts)
 from .attention import CacheView, PagedAttention
-from .block import OutputNormBlock, PreNormBlock
+from .block import GatedPreNormBlock, OutputNormBlock, PreNormBlock
 from .delta_rule import GeneralDeltaMixer
 from .feedforward import GatedMLP, PolyNormMLP
 from .gated_delta import GatedDeltaMixer
+from .latent import DifferentialAttention, LatentAttention
 from .linear import Linear
-from .model import BigramDecoderModel, DecoderModel
+from .model import BigramDecoderModel, DecoderModel, ReinjectDecoderModel
 from .norms import LayerNorm, RMSNorm
-from .positions import BucketedBias, NoPosition, Rotary, RotaryPairs, distance_bucket, rotary_inv_freq, rotary_tables
-from .recurrence import GatedLinearRecurrence, ParallelMixer
+from .positions import BucketedBias, NoPosition, PartialRotation, Rotary, RotaryPairs, distance_bucket, rotary_inv_freq, rotary_tables
+from .recurrence import GatedLinearRecurrence, MinGRU, ParallelMixer
 from .registry import (
     BLOCKS,
     FEEDFORWARDS,

@@ -6,6 +6,8 @@ whose spec has no feed-forward is the first half alone."""
 from __future__ import annotations
 
 from .. import kernels
+from ..weights.loader import ExpectedTensor
+from .linear import Linear
 from .registry import (
     build_feedforward,
     build_mixer,
@@ -137,6 +139,70 @@ class OutputNormBlock:
             nxt = self._next_input(residual, not last)
             self.ff_norm.accumulate(residual, m, nxt)
             ctx.residual_cast = nxt
+        return residual, None
+
+
+@register_block("gated_prenorm")
+class GatedPreNormBlock:
+    """``x += sigmoid(W1 h + b1) * mixer(h)`` with h = norm1(x), then ``x += sigmoid(W2 h + b2) * ff(h)`` with h =
+    norm2(x): a pre-norm block whose sublayers' results pass a gate per coordinate that reads what the sublayer reads.
+    The gate's product is in the activation type; the sigmoid, the product with the sublayer's result and the sum
+    into the residual are one float32 kernel.  A sublayer without a gate tensor is added as it is."""
+
+    @staticmethod
+    def expected_tensors(spec):
+        d = spec.mixer_norm.size
+        out = {}
+        out.update(norm_class(spec.mixer_norm).expected_tensors(spec.mixer_norm))
+        out.update(mixer_class(spec.mixer).expected_tensors(spec.mixer))
+        if spec.feedforward is not None:
+            out.update(norm_class(spec.ff_norm).expected_tensors(spec.ff_norm))
+            out.update(feedforward_class(spec.feedforward).expected_tensors(spec.feedforward))
+        for w, b, there in ((spec.mixer_gate, spec.mixer_gate_bias, True),
+                            (spec.ff_gate, spec.ff_gate_bias, spec.feedforward is not None)):
+            if there and w is not None:
+                out[w] = ExpectedTensor((d, d))
+                if b is not None:
+                    out[b] = ExpectedTensor((d,))
+        return out
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.rt = rt
+        self.mixer_norm = build_norm(spec.mixer_norm, tensors, rt)
+        self.mixer = build_mixer(spec.mixer, tensors, rt)
+        self.ff_norm = build_norm(spec.ff_norm, tensors, rt) if spec.feedforward is not None else None
+        self.feedforward = build_feedforward(spec.feedforward, tensors, rt) if spec.feedforward is not None else None
+
+        def gate(w, b, name):
+            if w is None:
+                return None, None
+            return Linear(tensors[w], rt, name), (tensors[b].contiguous() if b is not None else None)
+
+        self.mixer_gate, self.mixer_gate_bias = gate(spec.mixer_gate, spec.mixer_gate_bias, "mixer_gate")
+        self.ff_gate, self.ff_gate_bias = gate(spec.ff_gate, spec.ff_gate_bias, "ff_gate") \
+            if spec.feedforward is not None else (None, None)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feedforward) if p is not None)
+
+    def _add(self, residual, y, h, gate, bias):
+        if gate is None:
+            kernels.residual_add(residual, y)
+            return
+        g = gate(h, self.rt.ws.take("sublayer_gate", tuple(y.shape), self.rt.act_dtype))
+        kernels.gated_residual_add(residual, y, g, bias)
+
+    def forward(self, residual, pending, ctx, cache):
+        ctx.handover = None
+        ctx.upcoming_norm = None
+        ctx.residual_cast = None
+        h = self.mixer_norm.add_norm(residual, pending)
+        self._add(residual, self.mixer.forward(h, ctx, cache), h, self.mixer_gate, self.mixer_gate_bias)
+        if self.feedforward is not None:
+            h = self.ff_norm.add_norm(residual, None)
+            self._add(residual, self.feedforward.forward(h, ctx), h, self.ff_gate, self.ff_gate_bias)
         return residual, None
 
 

@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` (engine/llama_mlp.py:30-33).
+"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` (engine/llama_mlp.py:30-33); other activations of the
+gate, clamps of both branches and an offset of the up branch are options of the spec (``kernels.glu_act``).
 
 Gate and up are one matrix product over the row-concatenated weights
 [2*intermediate, hidden]; the activation and the product by ``up`` are one
@@ -32,8 +33,10 @@ class GatedMLP:
         }
 
     def __init__(self, spec, tensors, rt):
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not built")
+        if spec.activation not in kernels.GLU_KINDS:
+            raise ValueError(f"activation {spec.activation!r} is not built (known: {sorted(kernels.GLU_KINDS)})")
+        # the products' fused epilogues know silu(gate) * up only; any other activation is a kernel of its own
+        self.plain_silu = spec.activation == "silu" and spec.up_offset == 0.0
         self.spec = spec
         self.rt = rt
         gate, up = tensors[spec.gate_proj], tensors[spec.up_proj]
@@ -44,7 +47,7 @@ class GatedMLP:
         self.down = Linear(tensors[spec.down_proj], rt, "down")
 
     def can_fuse(self, n_tokens: int, norm) -> bool:
-        return (hasattr(norm, "fusable_rms") and self.gate_up.streams(n_tokens, normed=True)
+        return (self.plain_silu and hasattr(norm, "fusable_rms") and self.gate_up.streams(n_tokens, normed=True)
                 and self.down.streams(n_tokens))
 
     def forward_fused(self, residual: torch.Tensor, norm, ctx) -> None:
@@ -63,14 +66,18 @@ class GatedMLP:
         s, ws, dt = self.spec, self.rt.ws, self.rt.act_dtype
         h = ws.take("ff_hidden", (n, s.intermediate), dt)
         w = self.gate_up.weight
-        if (dt is torch.bfloat16 and w.dtype is torch.bfloat16 and n >= self.TCGEN05_MIN_ROWS
+        if (self.plain_silu and dt is torch.bfloat16 and w.dtype is torch.bfloat16 and n >= self.TCGEN05_MIN_ROWS
                 and kernels.gemm_tcgen05_supports(n, 2 * s.intermediate, s.hidden, x.stride(0), w.stride(0))):
             # gate/up on the tcgen05 tensor cores with silu(gate)*up in the epilogue: the [n, 2*intermediate]
             # matrix never goes to memory
             kernels.gemm_tcgen05(x, w, h, "silu_mul")
         else:
             gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
-            kernels.silu_mul(gu, h, interleaved=True)
+            if self.plain_silu:
+                kernels.silu_mul(gu, h, interleaved=True)
+            else:
+                kernels.glu_act(gu, h, s.activation, interleaved=True, alpha=s.act_alpha, limit=s.act_limit,
+                                up_offset=s.up_offset)
         return self.down(h, ws.take("ff_out", (n, s.hidden), dt))
 
 

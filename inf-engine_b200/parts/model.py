@@ -82,6 +82,10 @@ class DecoderModel:
         kernels.embed_gather(ctx.token_ids, self.embedding, residual)
         return residual
 
+    def before_entry(self, i: int, residual, pending, ctx):
+        """What a derived top level does to the stream right before schedule entry ``i`` runs; nothing here."""
+        return residual, pending
+
     def finish_logits(self, logits: torch.Tensor, ctx) -> torch.Tensor:
         """What a derived top level does to the head's float32 logits (in place) before they leave; nothing here."""
         return logits
@@ -102,6 +106,7 @@ class DecoderModel:
             nxt = self.layers[spec.schedule[i + 1].layer] if i < last else None
             ctx.norm_after_block = getattr(nxt, "mixer_norm", None) if nxt is not None else self.final_norm
             ctx.last_block = i == last
+            residual, pending = self.before_entry(i, residual, pending, ctx)
             residual, pending = self.layers[e.layer].forward(residual, pending, ctx, self._views[i])
         ctx.norm_after_block = None
         m = ctx.n_logits
@@ -163,3 +168,35 @@ class BigramDecoderModel(DecoderModel):
                              self.bigram, self._prev_token, residual, s.bigram_buckets, s.bigram_mul_prev,
                              s.bigram_mul_cur)
         return residual
+
+
+@register_model("reinject_decoder")
+class ReinjectDecoderModel(DecoderModel):
+    """``DecoderModel`` whose token embedding is multiplied by a constant and added to the residual stream again right
+    before the schedule entries that the spec names (``ReinjectDecoderSpec``): the scaled embedding of the step's
+    tokens is kept in a buffer of its own beside the stream."""
+
+    def __init__(self, spec, tensors: dict, rt):
+        super().__init__(spec, tensors, rt)
+        self.reinject = frozenset(int(i) for i in spec.reinject_before)
+        for i in self.reinject:
+            if not 0 < i < len(spec.schedule):
+                raise ValueError(f"the embedding cannot be added again before schedule entry {i}")
+        self._embedded = None
+
+    def embed(self, ctx) -> torch.Tensor:
+        residual = super().embed(ctx)
+        self._embedded = self.rt.ws.take("embedded", tuple(residual.shape), torch.float32) if self.reinject else None
+        if self.spec.embedding_scale != 1.0 or self._embedded is not None:
+            kernels.scale_rows(residual, self.spec.embedding_scale, self._embedded)
+        return residual
+
+    def before_entry(self, i: int, residual, pending, ctx):
+        if i not in self.reinject:
+            return residual, pending
+        if pending is not None:
+            kernels.residual_add(residual, pending)
+        kernels.residual_add(residual, self._embedded)
+        ctx.handover = None
+        ctx.residual_cast = None
+        return residual, None

@@ -2,7 +2,8 @@
 float32 statistics whatever the activation dtype, fused with the residual sum
 that precedes it in a pre-norm block (engine/llama_block.py:53-62).  With
 ``unit_offset`` the stored tensor lies around zero and the gain is one plus it
-(formed once, in float32).  ``accumulate`` is the norm of a block that norms its
+(formed once, in float32); with ``scalar`` the stored tensor is a single number that multiplies every coordinate.
+``accumulate`` is the norm of a block that norms its
 sublayers' OUTPUTS: the normed rows are added into the residual.
 LayerNorm: ``(x - mean) / sqrt(variance + eps) * weight + bias`` with the variance
 the mean of the squared deviations, the same way."""
@@ -20,12 +21,16 @@ from .registry import register_norm
 class RMSNorm:
     @staticmethod
     def expected_tensors(spec):
-        return {spec.weight: ExpectedTensor((spec.size,), init="gain")}
+        return {spec.weight: ExpectedTensor(() if getattr(spec, "scalar", False) else (spec.size,), init="gain")}
 
     def __init__(self, spec, tensors, rt):
         self.spec = spec
         self.rt = rt
         self.gain = tensors[spec.weight]
+        if getattr(spec, "scalar", False):
+            # one number for every coordinate: spread out once, so that the kernels and the products that apply a norm
+            # in their prologue see the vector they expect
+            self.gain = self.gain.reshape(1).expand(spec.size).contiguous()
         if getattr(spec, "unit_offset", False):
             self.gain = (1.0 + self.gain.float()).contiguous()
         self.eps = float(spec.eps)

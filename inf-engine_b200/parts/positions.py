@@ -113,6 +113,57 @@ class RotaryPairs:
         return None
 
 
+def partial_rotation_frequencies(spec) -> tuple[torch.Tensor, float]:
+    """(float64 frequencies [rot_dims / 2] on the CPU, multiplier of cosine and sine) of a ``rotary_partial`` spec:
+    ``theta^(-2i / rot_dims)``, blended for a longer context when the spec carries a ``yarn`` entry."""
+    dims = spec.rot_dims
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(spec.theta) ** (-2.0 * i / dims)
+    y = spec.yarn
+    if y is None:
+        return f, 1.0
+    ln_base = math.log(float(spec.theta))
+
+    def dim_of(turns: float) -> float:       # the (fractional) pair index whose wavelength makes that many turns in the original context
+        return dims * math.log(y.original / (2.0 * math.pi * turns)) / (2.0 * ln_base)
+
+    lo = max(math.floor(dim_of(y.fast)), 0)
+    hi = min(math.ceil(dim_of(y.slow)), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / y.factor * ramp + f * (1.0 - ramp), y.mult_slope * math.log(y.factor) + 1.0
+
+
+@register_position("rotary_partial")
+class PartialRotation:
+    """``rot_dims`` dimensions of a head turn by ``position * frequency``, paired in halves or as neighbours; which
+    dimensions of the head these are is the mixer's business (``kernels.head_prepare`` takes an offset).  No table: the
+    kernel forms the angle from the position and the float64 frequencies, so positions have no limit."""
+
+    @staticmethod
+    def expected_tensors(spec):
+        return {}
+
+    def __init__(self, spec, tensors, rt):
+        if spec.rot_dims % 2 or spec.rot_dims <= 0:
+            raise ValueError(f"a rotation needs an even, positive number of dimensions, not {spec.rot_dims}")
+        if spec.layout not in ("halves", "neighbours"):
+            raise ValueError(f"rotation layout {spec.layout!r} is not built (known: halves, neighbours)")
+        self.spec = spec
+        key = ("rotary_partial", spec.theta, spec.rot_dims, spec.yarn)
+        if key not in rt.shared:
+            f, mult = partial_rotation_frequencies(spec)
+            rt.shared[key] = (f.to(rt.device), float(mult))
+        self.inv_freq, self.mult = rt.shared[key]
+        self.rot_dims = spec.rot_dims
+        self.neighbours = spec.layout == "neighbours"
+
+    def rotary_tables(self):
+        return None
+
+    def rotate(self, q, k, ctx):
+        return None
+
+
 def distance_bucket(n: int, n_buckets: int, max_distance: int) -> int:
     """Row of a bucketed distance table for a key that lies ``n`` positions back.
 

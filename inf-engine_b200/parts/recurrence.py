@@ -102,6 +102,47 @@ class GatedLinearRecurrence:
         return self.o(mixed, rt.ws.take("mixer_out", (n, self.spec.hidden), rt.act_dtype))
 
 
+@register_mixer("mingru")
+class MinGRU:
+    """A gated recurrence whose gates read the current token only (``MinGRUSpec``): one product for z, u and the
+    output gate, one scan kernel from there to ``S * silu(gate)`` in float32 (``csrc/gating.cu``), the output product.
+    The state is one float32 vector a request; the step's tokens of every request run in order from the state the step
+    before left."""
+
+    graph_safe = True
+
+    @staticmethod
+    def expected_tensors(spec):
+        w = spec.width
+        return {
+            spec.z_proj: ExpectedTensor((w, spec.hidden)), spec.z_bias: ExpectedTensor((w,)),
+            spec.x_proj: ExpectedTensor((w, spec.hidden)), spec.x_bias: ExpectedTensor((w,)),
+            spec.gate_proj: ExpectedTensor((w, spec.hidden)),
+            spec.o_proj: ExpectedTensor((spec.hidden, w)),
+        }
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.rt = rt
+        ws = [tensors[spec.z_proj], tensors[spec.x_proj], tensors[spec.gate_proj]]
+        dtype = torch.float32 if any(w.dtype is torch.float32 for w in ws) else ws[0].dtype
+        self.proj = Linear(torch.cat([w.to(dtype) for w in ws], dim=0).contiguous(), rt, "mingru_proj")
+        self.z_bias, self.x_bias = same_dtype([tensors[spec.z_bias], tensors[spec.x_bias]])     # added in float32 by the scan
+        self.o = Linear(tensors[spec.o_proj], rt, "o")
+
+    def cache_requirement(self) -> CacheRequirement:
+        return CacheRequirement(kind="state", state_shape=(self.spec.width,), state_dtype=torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        n, w = x.shape[0], s.width
+        proj = self.proj(x, rt.ws.take("mingru_proj", (n, 3 * w), rt.act_dtype))
+        mixed = rt.ws.take("mingru_mixed", (n, w), rt.act_dtype)
+        kernels.mingru_scan(proj[:, :w], proj[:, w:2 * w], proj[:, 2 * w:], self.z_bias, self.x_bias, cache.state, mixed,
+                            ctx.q_start, ctx.slots, ctx.n_requests, write_state=cache.write)
+        return self.o(mixed, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
+
+
 @register_mixer("parallel")
 class ParallelMixer:
     @staticmethod
