@@ -151,11 +151,8 @@ def differential_attention(h, m: dict, w: dict, p: str, eps: float, round_to=Non
 def mingru(h, m: dict, w: dict, p: str, round_to=None, state=None):
     """Returns (output, final state); ``state`` [width] is where the sequence starts (zeros when None)."""
     T = h.shape[0]
-    z = torch.sigmoid(lin(w[p + "z"], h) + w[p + "z.b"].to(F))
-    u = lin(w[p + "x"], h) + w[p + "x.b"].to(F)
-    if round_to is not None:
-        z = torch.sigmoid(rnd(lin(w[p + "z"], h) + w[p + "z.b"].to(F), round_to))
-        u = rnd(u, round_to)
+    z = torch.sigmoid(lin(w[p + "z"], h, round_to) + w[p + "z.b"].to(F))      # the bias joins in full precision
+    u = lin(w[p + "x"], h, round_to) + w[p + "x.b"].to(F)
     cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
     s = torch.zeros(z.shape[1], dtype=F) if state is None else state.to(F).clone()
     out = torch.empty_like(z)
@@ -224,3 +221,14 @@ def forward(cfg: dict, w: dict, tokens, round_to=None, return_layers: bool = Fal
     h = scalar_norm(x, w["final.norm"], eps, round_to)
     logits = lin(w["head"], h)
     return (logits, torch.stack(seen)) if return_layers else logits
+
+
+def forward_float32(cfg: dict, w: dict, tokens):
+    """The same model with every operation in float32: how far it lies from the float64 result says how well
+    conditioned a sequence is (a row on which the two disagree says little about any implementation)."""
+    global F
+    F = torch.float32
+    try:
+        return forward(cfg, w, tokens).double()
+    finally:
+        F = torch.float64
