@@ -414,6 +414,33 @@ def _kipezen_configs(size):
     return kpz, _family_configs(size)[0]
 
 
+def _fovunex_configs(size):
+    """A Fovunex model of the size's width (a recurrence, differential attention in chunks of 1,024 positions with
+    values twice as large as a map, a recurrence, latent attention over rows of 192 compressed and 64 rotated numbers;
+    gated residual sums; a clamped feed-forward of three matrices) and the Kipezen model of equal width, depth and head
+    geometry, the closest family the engine had (rotated attention under a mask beside a gated recurrence with a float32
+    state)."""
+    from inf_engine_b200.config import parse_config_dict
+    z = FAMILY_SIZES[size]
+    w, H, G, inter = z["width"], z["heads"], z["kv"], z["inter"]
+    mlp = {"kind": "dense", "ff": inter, "limit": 7.0}
+    gru = {"type": "mingru", "mixer": {"width": w}, "mlp": mlp}
+    diff = {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": H // 2, "kv_heads": G // 2, "dim": FAMILY_HD, "vdim": 2 * FAMILY_HD, "scale": FAMILY_HD ** -0.5,
+                      "diff": 0.8, "rot": {"base": 10000.0, "dims": FAMILY_HD // 2}, "mask": {"size": FOVUNEX_CHUNK}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": H, "dim": FAMILY_HD, "rot_dim": FOVUNEX_ROT, "vdim": FAMILY_HD, "kv_rank": FOVUNEX_RANK,
+                     "scale": (FAMILY_HD + FOVUNEX_ROT) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": FOVUNEX_ROT,
+                             "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    fvx = parse_config_dict({"architecture": "Fovunex", "vocab": FAMILY_VOCAB, "width": w, "norm": {"eps": 1e-5},
+                             "embedding": {"scale": float(w) ** 0.5}, "layers": [gru, diff, gru, lat]})
+    return fvx, _kipezen_configs(size)[0]
+
+
+FOVUNEX_CHUNK, FOVUNEX_RANK, FOVUNEX_ROT = 1024, 192, 64
+
+
 def _weight_bytes(runner):
     seen, n = set(), 0
     import torch
@@ -439,8 +466,8 @@ def run_family(args):
     from inf_engine_b200 import Engine, StepEntry, SamplingConfig, kernels
     from inf_engine_b200.sampling import pack_rows, request_key
 
-    if args.family not in ("barerax", "kipezen"):
-        print(f"--family {args.family}: unknown (known: barerax, kipezen)")
+    if args.family not in ("barerax", "kipezen", "fovunex"):
+        print(f"--family {args.family}: unknown (known: barerax, kipezen, fovunex)")
         return 2
     pk = peaks()
     torch.cuda.set_device(0)
@@ -818,8 +845,167 @@ def run_family(args):
             n_chosen * 2 * ffe * W * 2, 2 * inter * W * 2)
         return rows
 
+    def fovunex_kernel_table(size):
+        """Every kernel that the Fovunex family added, alone, beside the like kernel of the closest family (Kipezen, or
+        the Llama path where Kipezen has none), at 2,048 tokens of one request and at 8 requests of one token over
+        2,048 keys."""
+        from inf_engine_b200.engine.batch import KVGroupContext, StepContext
+        from inf_engine_b200.parts import CacheView, Runtime
+        from inf_engine_b200.parts.attention import PagedAttention
+        from inf_engine_b200.parts.latent import attend_float32
+        z = FAMILY_SIZES[size]
+        W, H, G, hd, inter = z["width"], z["heads"], z["kv"], FAMILY_HD, z["inter"]
+        N, B, dev, bf = PROMPT_LEN, 8, "cuda", torch.bfloat16
+        g = torch.Generator(device=dev).manual_seed(1)
+        rnd = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.5)
+        i32 = lambda v: torch.as_tensor(v, dtype=torch.int32, device=dev)
+        rows = []
+
+        def add(name, like, ms, ms_like, nbytes=None, nbytes_like=None, flops=None, flops_like=None, note=None):
+            rec = {"kernel": name, "like": like, "ms": ms, "like_ms": ms_like}
+            if nbytes is not None:
+                rec["frac_of_hbm"] = nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+                if ms_like:
+                    rec["like_frac_of_hbm"] = (nbytes_like or nbytes) / (ms_like * 1e-3) / 1e9 / pk["hbm_gbs"]
+            if flops is not None:
+                rec["frac_of_bf16"] = flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+                if ms_like:
+                    rec["like_frac_of_bf16"] = (flops_like or flops) / (ms_like * 1e-3) / 1e12 / pk["bf16_tflops"]
+            if note:
+                rec["note"] = note
+            rows.append(rec)
+
+        rt = Runtime(dev, bf)
+        n_pages = B * N // PAGE
+        qs1, sl1 = i32([0, N]), i32([0])
+        qs8, sl8 = torch.arange(B + 1, dtype=torch.int32, device=dev), torch.arange(B, dtype=torch.int32, device=dev)
+
+        def context(q_lens, before):
+            ctx = StepContext(rt, PAGE)
+            R, n = len(q_lens), sum(q_lens)
+            ctx.n_tokens, ctx.n_requests, ctx.n_logits = n, R, 0
+            starts = [0]
+            for ql in q_lens:
+                starts.append(starts[-1] + ql)
+            per = n_pages // R
+            ctx.q_start, ctx.ctx_before = i32(starts), i32(before)
+            ctx.positions = i32([b + t for ql, b in zip(q_lens, before) for t in range(ql)])
+            ctx.slots = i32(list(range(R)))
+            table_ = torch.arange(per * R, dtype=torch.int32, device=dev).view(R, per)
+            sm = i32([(r * per + (b + t) // PAGE) * PAGE + (b + t) % PAGE for r, (ql, b) in enumerate(zip(q_lens, before)) for t in range(ql)])
+            ctx.kv = [KVGroupContext(sm, table_)]
+            ctx.host = {"q_lens": list(q_lens), "ctx_before": list(before), "q_start": starts}
+            ctx.max_q_len, ctx.max_seq_len = max(q_lens), max(b + ql for ql, b in zip(q_lens, before))
+            ctx.keys_cap = ctx.max_seq_len
+            return ctx
+
+        ctx_p, ctx_d = context([N], [0]), context([1] * B, [N - 1] * B)
+        # the gated sum into the residual | the norm of a sublayer's output into the residual (Kipezen)
+        res, y, gpre, gb = rnd(N, W), rnd(N, W).to(bf), rnd(N, W).to(bf), rnd(W).to(bf)
+        nxt, gain = torch.empty(N, W, device=dev, dtype=bf), (1 + 0.1 * rnd(W))
+        add("gated sum into the residual", "output norm into the residual (+ next input)",
+            timed(lambda: kernels.gated_residual_add(res, y, gpre, gb)),
+            timed(lambda: kernels.outnorm_accumulate(res, y, gain, 1e-5, nxt)), N * W * (4 + 4 + 2 + 2), N * W * (4 + 4 + 2 + 2))
+        # the clamped activation of the feed-forward | SiLU(gate) * up (the Llama path's elementwise pass)
+        gu, h2 = rnd(N, 2 * inter).to(bf), torch.empty(N, inter, device=dev, dtype=bf)
+        add("clamped gate * sigmoid(1.702 gate) * (up + 1)", "silu_mul",
+            timed(lambda: kernels.glu_act(gu, h2, "clamped_swish", interleaved=True, alpha=1.702, limit=7.0, up_offset=1.0)),
+            timed(lambda: kernels.silu_mul(gu, h2, interleaved=True)), N * inter * 6)
+        # the minGRU scan | the linear recurrent unit's scan (Kipezen)
+        zug, zb = rnd(N, 3 * W).to(bf), rnd(W).to(bf)
+        sst, rout = torch.zeros(16, W, device=dev), torch.empty(N, W, device=dev, dtype=bf)
+        u, ypre, gates, lam = rnd(N, W).to(bf), rnd(N, W).to(bf), rnd(N, 2 * W), rnd(W).to(bf)
+        scan = lambda n, qs, sl, R: kernels.mingru_scan(zug[:n, :W], zug[:n, W:2 * W], zug[:n, 2 * W:], zb, zb, sst, rout[:n], qs, sl, R)
+        lru = lambda n, qs, sl, R: kernels.linear_recurrence(u[:n], ypre[:n], gates[:n, :W], gates[:n, W:], zb, zb, lam, sst, rout[:n],
+                                                             qs, sl, R, 8.0)
+        add("minGRU scan, prompt of 2,048 tokens (one request)", "linear recurrent unit scan, prompt",
+            timed(lambda: scan(N, qs1, sl1, 1), reps=5), timed(lambda: lru(N, qs1, sl1, 1), reps=5),
+            N * W * (3 * 2 + 2), N * W * (2 + 2 + 4 + 4 + 2), note="a scan over tokens, a channel a thread")
+        add("minGRU scan, decode b8", "linear recurrent unit scan, decode",
+            timed(lambda: scan(B, qs8, sl8, B)), timed(lambda: lru(B, qs8, sl8, B)),
+            B * W * (3 * 2 + 2 + 8), B * W * (2 + 2 + 4 + 4 + 2 + 8))
+        # differential attention: H/2 heads of two maps of 64 over values of 128; G/2 key heads of two maps
+        Hd, Gd, dv = H // 2, G // 2, 2 * hd
+        qkv = rnd(N, (H + G) * hd + Gd * dv).to(bf)
+        q, kx, v = qkv[:, :H * hd], qkv[:, H * hd:(H + G) * hd], qkv[:, (H + G) * hd:]
+        kpool = torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf)
+        vpool = torch.zeros(n_pages, Gd, PAGE, dv, device=dev, dtype=bf)
+        hg = (1 + 0.1 * rnd(hd)).to(bf)
+        inv_freq = (10000.0 ** (-2.0 * torch.arange(hd // 4, dtype=torch.float64) / (hd // 2))).to(dev)
+        # Kipezen's like kernels work on H heads of 64 over G key heads, keys and values of 64
+        qkv_k = rnd(N, (H + 2 * G) * hd).to(bf)
+        q_k, k_k, v_k = qkv_k[:, :H * hd], qkv_k[:, H * hd:(H + G) * hd], qkv_k[:, (H + G) * hd:]
+        kpool_k, vpool_k = torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf), torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf)
+        qb, kb, vb = rnd(H * hd).to(bf), rnd(G * hd).to(bf), rnd(G * hd).to(bf)
+        qg, kg = (1 + 0.1 * rnd(H * hd)).to(bf), (1 + 0.1 * rnd(G * hd)).to(bf)
+        like_prepare = timed(lambda: kernels.rownorm_rotate_write(q_k, k_k, v_k, qb, kb, vb, qg, kg, 1e-5, inv_freq, hd // 2, ctx_p.positions,
+                                                                  ctx_p.kv[0].slot_mapping, kpool_k, vpool_k, H, G, hd, hd, PAGE))
+        add("map norms + rotation in halves + cache write (differential)", "biases + whole-row norm + pair rotation + cache write",
+            timed(lambda: kernels.head_prepare(q, H, hd, kx, G, hd, ctx_p.positions, ctx_p.kv[0].slot_mapping, kpool, PAGE, q_gain=hg,
+                                               q_norm_dims=hd, k_gain=hg, k_norm_dims=hd, eps=1e-5, inv_freq=inv_freq, rot_dims=hd // 2,
+                                               v=v, vpool=vpool, n_v_heads=Gd, v_head_dim=dv)),
+            like_prepare, N * ((H + G) * hd * 2 + Gd * dv) * 2 * 1.0 + N * G * hd * 2, N * (H + 2 * G) * hd * 2 * 2)
+        kpz = _kipezen_configs(size)[0]
+        spec_k = kpz.model_spec().layers[3].mixer.branches[0]
+        tensors = {n: ((1 + 0.1 * rnd(*e.shape)) if e.init == "gain" else rnd(*e.shape) * 0.1).to(bf)
+                   for n, e in PagedAttention.expected_tensors(spec_k).items()}
+        att_k = PagedAttention(spec_k, tensors, rt)
+        view_k = CacheView("kv", 0, kpool_k, vpool_k, None, True)
+        out_k = torch.empty(N, H * hd, device=dev, dtype=bf)
+        like_att = lambda ctx, n: att_k._attend(q_k[:n], out_k[:n], view_k, ctx, ctx.kv[0], head_scale=att_k.head_scale)
+        window = 1024
+        pairs_all = N * (N + 1) // 2
+        pairs_k = pairs_all - (N - window) * (N - window + 1) // 2 + 4 * (N - window - 4)
+        like_prompt, like_decode = timed(lambda: like_att(ctx_p, N), reps=5), timed(lambda: like_att(ctx_d, B))
+        like_prompt_flops, like_decode_bytes = 4 * H * hd * pairs_k, B * (window + 4) * G * hd * 2 * 2
+        maps = torch.empty(N, H * dv, device=dev, dtype=bf)
+        diff_att = lambda ctx, n: attend_float32(q[:n], maps[:n], kpool, vpool, ctx, ctx.kv[0], H, G, hd, dv, hd ** -0.5, FOVUNEX_CHUNK,
+                                                  n_v_heads=Gd)
+        pairs_c = (N // FOVUNEX_CHUNK) * FOVUNEX_CHUNK * (FOVUNEX_CHUNK + 1) // 2
+        add("attention, prompt (two maps a head, chunks of 1,024, float32 scores)", "attention, prompt (window of 1,024 + 4 kept keys)",
+            timed(lambda: diff_att(ctx_p, N), reps=5), like_prompt, flops=2 * H * (hd + dv) * pairs_c, flops_like=like_prompt_flops)
+        add("attention, decode b8 x 2,048 keys (two maps a head, 1,024 visible)", "attention, decode (1,028 visible)",
+            timed(lambda: diff_att(ctx_d, B)), like_decode, B * FOVUNEX_CHUNK * (G * hd + Gd * dv) * 2, like_decode_bytes)
+        gate_, dout = rnd(N, Hd * dv).to(bf), torch.empty(N, Hd * dv, device=dev, dtype=bf)
+        add("maps' difference + head norm + output gate", "silu_mul",
+            timed(lambda: kernels.diff_combine(maps, gate_, dout, Hd, Gd, dv, 0.7, 1e-5, 0.2)), rows[1]["like_ms"],
+            N * Hd * dv * (2 * 2 + 2 + 2), N * inter * 6)
+        # latent attention: H heads of 64 + 64 rotated over one cached row of 192 + 64 a token
+        kr, r = FOVUNEX_RANK, FOVUNEX_ROT
+        qd, rd = hd + r, kr + r
+        ql, row = rnd(N, H * qd).to(bf), rnd(N, rd).to(bf)
+        lpool = torch.zeros(n_pages, 1, PAGE, rd, device=dev, dtype=bf)
+        lg = (1 + 0.1 * rnd(kr)).to(bf)
+        inv_l = (10000.0 ** (-2.0 * torch.arange(r // 2, dtype=torch.float64) / r)).to(dev)
+        add("compressed-row norm + rotation of neighbours + cache write (latent)", "biases + whole-row norm + pair rotation + cache write",
+            timed(lambda: kernels.head_prepare(ql, H, qd, row, 1, rd, ctx_p.positions, ctx_p.kv[0].slot_mapping, lpool, PAGE, k_gain=lg,
+                                               k_norm_dims=kr, eps=1e-5, inv_freq=inv_l, rot_dims=r, q_rot_off=hd, k_rot_off=kr,
+                                               neighbours=True, mult=1.1)),
+            like_prepare, N * (H * qd * 2 + rd * 2) * 2, N * (H + 2 * G) * hd * 2 * 2)
+        absorb, qc = (rnd(H, qd, rd) * 0.1).to(bf), torch.empty(N, H * rd, device=dev, dtype=bf)
+        ag, gts = rnd(W // 256, 256, 256).to(bf), torch.empty(N, W, device=dev)
+        like_hg = timed(lambda: kernels.gemm_simt_batched(u, ag, gts))
+        rec = {"kernel": "queries into the compressed space, a product a head (float32 on CUDA cores), prompt",
+               "like": "block-diagonal gate product, prompt (float32 on CUDA cores)"}
+        rec["ms"], rec["like_ms"] = timed(lambda: kernels.heads_gemm(ql, qd, absorb, qc, rd)), like_hg
+        rec["tflops_f32"], rec["like_tflops_f32"] = 2 * N * H * qd * rd / (rec["ms"] * 1e-3) / 1e12, 2 * N * W * 256 / (like_hg * 1e-3) / 1e12
+        rows.append(rec)
+        expand, mixed, heads = (rnd(H, kr, hd) * 0.1).to(bf), torch.empty(N, H * kr, device=dev, dtype=bf), torch.empty(N, H * hd, device=dev, dtype=bf)
+        rec = {"kernel": "values out of the compressed space, a product a head, prompt", "like": rec["like"], "like_ms": like_hg,
+               "like_tflops_f32": rec["like_tflops_f32"]}
+        rec["ms"] = timed(lambda: kernels.heads_gemm(mixed, kr, expand, heads, hd))
+        rec["tflops_f32"] = 2 * N * H * kr * hd / (rec["ms"] * 1e-3) / 1e12
+        rows.append(rec)
+        lat_att = lambda ctx, n: attend_float32(qc[:n], mixed[:n], lpool, lpool, ctx, ctx.kv[0], H, 1, rd, kr, qd ** -0.5, None,
+                                                n_v_heads=1, v_row=rd)
+        add("attention, prompt (latent: %d heads over one row of %d, every key)" % (H, rd), "attention, prompt (window of 1,024 + 4 kept keys)",
+            timed(lambda: lat_att(ctx_p, N), reps=5), like_prompt, flops=2 * H * (rd + kr) * pairs_all, flops_like=like_prompt_flops)
+        add("attention, decode b8 x 2,048 keys (latent)", "attention, decode (1,028 visible)",
+            timed(lambda: lat_att(ctx_d, B)), like_decode, B * N * rd * 2, like_decode_bytes)
+        return rows
+
     sizes = {}
-    if args.family == "kipezen" and args.family_step:
+    if args.family in ("kipezen", "fovunex") and args.family_step:
         # one step launched kernel by kernel (no graphs) between cudaProfilerStart / Stop, for a launch list:
         #   ncu --metrics gpu__time_duration.sum --clock-control none --profile-from-start off --csv --log-file L \
         #       python bench.py --family kipezen --family-sizes w2048 --family-step decode
@@ -827,7 +1013,7 @@ def run_family(args):
         from inf_engine_b200 import ModelRunner
         from inf_engine_b200.weights import write_random_model
         size = (args.family_sizes or "w2048").split(",")[0]
-        kpz, _ = _kipezen_configs(size)
+        kpz, _ = (_kipezen_configs if args.family == "kipezen" else _fovunex_configs)(size)
         with tempfile.TemporaryDirectory() as tmp:
             write_random_model(kpz, args.seed, tmp)
             r = ModelRunner.from_dir(tmp, dtype="bfloat16", page_size=PAGE, n_pages=(args.batch + 1) * POOL_CONTEXT // PAGE,
@@ -853,7 +1039,24 @@ def run_family(args):
         torch.cuda.synchronize()
         torch.cuda.cudart().cudaProfilerStop()
         clocks.stop()
-        print(json.dumps({"impl": "ours", "family": "kipezen", "step": args.family_step, "size": size, "launches": kernels.LAUNCHES}))
+        print(json.dumps({"impl": "ours", "family": args.family, "step": args.family_step, "size": size, "launches": kernels.LAUNCHES}))
+        return 0
+    if args.family == "fovunex":
+        for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
+            fvx, kpz = _fovunex_configs(size)
+            rec = {"fovunex": model_numbers_of(fvx, args.batch), "kipezen": model_numbers_of(kpz, args.batch)}
+            rec["kernels"] = fovunex_kernel_table(size)
+            sizes[size] = rec
+        clocks.stop()
+        print(json.dumps({"impl": "ours", "family": "fovunex", "dtype": "bf16", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3),
+                          "data": "synthetic: seeded random weights, uniform random prompt ids",
+                          "config": {"layers": FAMILY_LAYERS, "pattern": "minGRU, differential attention, minGRU, latent attention",
+                                     "vocab": FAMILY_VOCAB, "head_dim": FAMILY_HD, "prompt": PROMPT_LEN, "decode_batch": args.batch,
+                                     "page_size": PAGE, "chunk": FOVUNEX_CHUNK, "kv_rank": FOVUNEX_RANK, "rot_dim": FOVUNEX_ROT,
+                                     "l2": "a 256 MB buffer is written before every timed kernel; model steps stream their weights",
+                                     "sizes": FAMILY_SIZES},
+                          "peaks": pk, "sizes": sizes, "clocks": clocks.summary(t_all0, time.perf_counter())}))
         return 0
     if args.family == "kipezen":
         for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
@@ -1073,11 +1276,11 @@ def main():
     ap.add_argument("--no-workloads", action="store_true",
                     help="leave out the two continuous-batching workloads at the other models' sizes")
     ap.add_argument("--family", default=None, metavar="NAME",
-                    help="instead of the default workload: prefill and decode of another model family (barerax, kipezen) at sizes like "
-                         "a real model's layers, beside a Llama model of equal size, and its kernels beside the like ones")
+                    help="instead of the default workload: prefill and decode of another model family (barerax, kipezen, fovunex) at sizes like "
+                         "a real model's layers, beside the closest earlier model of equal size, and its kernels beside the like ones")
     ap.add_argument("--family-sizes", default=None, help="comma-separated subset of the family's sizes (w1024,w2048)")
     ap.add_argument("--family-step", default=None, choices=["decode", "prefill"],
-                    help="with --family kipezen: run one such step kernel by kernel between cudaProfilerStart/Stop (for a launch list) and exit")
+                    help="with --family kipezen or fovunex: run one such step kernel by kernel between cudaProfilerStart/Stop (for a launch list) and exit")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
                     help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()
