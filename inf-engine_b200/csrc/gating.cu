@@ -82,11 +82,61 @@ __global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, in
   out[i] = from_f32<T>(a * (u + up_offset));
 }
 
+// bfloat16, eight outputs a thread (inter and the row stride multiples of 8, rows that start on 16 bytes)
+__global__ void glu_act_bf16_vec_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int inter, int in_stride,
+                                        size_t total8, int interleaved, int kind, float alpha, float limit, float up_offset) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const int per_row = inter >> 3;
+  const size_t n = idx / per_row;
+  const int j = (int)(idx - n * per_row) * 8;
+  const bf16* row = in + n * in_stride;
+  float g[8], u[8];
+  const uint4 a = *reinterpret_cast<const uint4*>(interleaved ? row + 2 * j : row + j);
+  const uint4 b = *reinterpret_cast<const uint4*>(interleaved ? row + 2 * j + 8 : row + inter + j);
+  const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 x = __bfloat1622float2(ap[t]), y = __bfloat1622float2(bp[t]);
+    if (interleaved) {
+      g[t] = x.x; u[t] = x.y; g[4 + t] = y.x; u[4 + t] = y.y;
+    } else {
+      g[2 * t] = x.x; g[2 * t + 1] = x.y; u[2 * t] = y.x; u[2 * t + 1] = y.y;
+    }
+  }
+  float r[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    float gg = g[t], uu = u[t], act;
+    if (kind == 1) {
+      gg = fminf(gg, limit);
+      uu = fminf(fmaxf(uu, -limit), limit);
+      act = gg * sigmoid_f(alpha * gg);
+    } else {
+      act = gg * sigmoid_f(gg);
+    }
+    r[t] = act * (uu + up_offset);
+  }
+  uint4 o;
+  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) op[t] = __floats2bfloat162_rn(r[2 * t], r[2 * t + 1]);
+  *reinterpret_cast<uint4*>(out + n * inter + j) = o;
+}
+
 extern "C" int ie_glu_act(const void* in, void* out, int n_rows, int inter, int in_stride, int interleaved, int kind,
                           float alpha, float limit, float up_offset, int act_dtype, cudaStream_t stream) {
   const size_t total = (size_t)n_rows * inter;
   if (total == 0) return IE_OK;
   if (kind < 0 || kind > 1) return IE_BAD_SIZE;
+  if (act_dtype == IE_BF16 && inter % 8 == 0 && in_stride % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+    const size_t total8 = total / 8;
+    return launch_k(glu_act_bf16_vec_kernel, (unsigned)((total8 + 255) / 256), 256, 0, stream, (const bf16*)in, (bf16*)out,
+                    inter, in_stride, total8, interleaved, kind, alpha, limit, up_offset);
+  }
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (act_dtype == IE_F32)
     return launch_k(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, inter, in_stride, total,

@@ -29,9 +29,8 @@ constexpr unsigned TC_SPIN_LIMIT = 1u << 20;
 
 __device__ int g_tc_error = 0;
 
-// silu(g) = g / (1 + e^-g) in float32 with ex2.approx and the approximate division: a relative error near 1e-6,
-// where the bfloat16 result keeps 4e-3; the precise forms cost the gate/up product 6 % of its time
-__device__ __forceinline__ float tc_silu(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+// silu(g) = g / (1 + e^-g) in float32 with ex2.approx and the approximate division (tc_glu below): a relative error
+// near 1e-6, where the bfloat16 result keeps 4e-3; the precise forms cost the gate/up product 6 % of its time
 
 struct TcParams {
   void* C;
@@ -39,7 +38,18 @@ struct TcParams {
   int epi;
   int n_stages;
   int staged;   // the output's base and row pitch are multiples of 16 bytes: full tiles leave through shared memory
+  // SILU_MUL with options: g' = min(g, act_limit), u' = clamp(u, -act_limit, act_limit); g' sigmoid(act_alpha g') (u' + up_offset)
+  int act_general;
+  float act_alpha, act_limit, up_offset;
 };
+
+// the gated activation of the SILU_MUL epilogue: silu(g) * u, or with the options above
+__device__ __forceinline__ float tc_glu(const TcParams& p, float g, float u) {
+  if (!p.act_general) return __fdividef(g, 1.f + __expf(-g)) * u;
+  g = fminf(g, p.act_limit);
+  u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+  return __fdividef(g, 1.f + __expf(-p.act_alpha * g)) * (u + p.up_offset);
+}
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tc_mbar_init(uint32_t bar, int count) {
@@ -124,7 +134,7 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, int m, int 
           for (int q = 0; q < 4; ++q) {
             const float g0 = __uint_as_float(r[j * 16 + 4 * q]), u0 = __uint_as_float(r[j * 16 + 4 * q + 1]);
             const float g1 = __uint_as_float(r[j * 16 + 4 * q + 2]), u1 = __uint_as_float(r[j * 16 + 4 * q + 3]);
-            vp[q] = __floats2bfloat162_rn(tc_silu(g0) * u0, tc_silu(g1) * u1);
+            vp[q] = __floats2bfloat162_rn(tc_glu(p, g0, u0), tc_glu(p, g1, u1));
           }
           *reinterpret_cast<uint4*>(dst + j * 8) = v;
         }
@@ -133,7 +143,7 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, int m, int 
         for (int j = 0; j < 32; j += 2) {
           if (n + j + 1 < p.N) {
             const float g = __uint_as_float(r[j]), u = __uint_as_float(r[j + 1]);
-            dst[j >> 1] = __float2bfloat16_rn(tc_silu(g) * u);
+            dst[j >> 1] = __float2bfloat16_rn(tc_glu(p, g, u));
           }
         }
       }
@@ -168,7 +178,7 @@ constexpr int TC_STAGE_BYTES = 32 * 128;      // per epilogue warp
 __device__ __forceinline__ int tc_out_bytes32(int epi) { return epi == TC_EPI_BF16 ? 64 : (epi == TC_EPI_SILU_MUL ? 32 : 128); }
 
 // this lane's 32 accumulator columns -> its row of the warp's tile, from byte offset off
-__device__ __forceinline__ void tc_stage_row(unsigned char* stage, int lane, int off, int epi, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tc_stage_row(const TcParams& p, unsigned char* stage, int lane, int off, int epi, const uint32_t (&r)[32]) {
   unsigned char* row = stage + lane * 128;
   const int u0 = off >> 4, sw = lane & 7;
   if (epi == TC_EPI_BF16) {
@@ -190,7 +200,7 @@ __device__ __forceinline__ void tc_stage_row(unsigned char* stage, int lane, int
       for (int q = 0; q < 4; ++q) {
         const float g0 = __uint_as_float(r[j * 16 + 4 * q]), u0f = __uint_as_float(r[j * 16 + 4 * q + 1]);
         const float g1 = __uint_as_float(r[j * 16 + 4 * q + 2]), u1f = __uint_as_float(r[j * 16 + 4 * q + 3]);
-        vp[q] = __floats2bfloat162_rn(tc_silu(g0) * u0f, tc_silu(g1) * u1f);
+        vp[q] = __floats2bfloat162_rn(tc_glu(p, g0, u0f), tc_glu(p, g1, u1f));
       }
       *reinterpret_cast<uint4*>(row + (((u0 + j) ^ sw) << 4)) = v;
     }
@@ -349,7 +359,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
           if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
         }
         if (staged) {
-          tc_stage_row(stage, lane, off, p.epi, r);
+          tc_stage_row(p, stage, lane, off, p.epi, r);
           off += out32;
           if (off == 128) {
             __syncwarp();
@@ -436,8 +446,11 @@ extern "C" int ie_gemm_tcgen05_supports(int M, int N, int K, int lda, int ldw) {
 
 // epi: 0 bf16 out [M,N]; 2 float32 C[M,N] += product; 3 silu(gate)*up over interleaved weight rows, bf16 out [M, N/2]
 // bn:  tile width, 128 or 256
-extern "C" int ie_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
-                               int epi, int bn, int n_sms, cudaStream_t stream) {
+// act_general != 0: the SILU_MUL epilogue clamps the gate from above and the up branch to [-act_limit, act_limit], scales
+// the sigmoid's argument by act_alpha and adds up_offset to the up branch
+extern "C" int ie_gemm_tcgen05_act(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                                   int epi, int bn, int n_sms, int act_general, float act_alpha, float act_limit,
+                                   float up_offset, cudaStream_t stream) {
   if (n_sms <= 0) return IE_BAD_SIZE;
   if (M <= 0 || N <= 0) return IE_OK;
   if (!ie_gemm_tcgen05_supports(M, N, K, lda, ldw)) return IE_BAD_SIZE;
@@ -452,6 +465,12 @@ extern "C" int ie_gemm_tcgen05(const void* A, const void* W, void* C, int M, int
   if (rc) return rc;
   TcParams p;
   p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.epi = epi; p.n_stages = 0;
+  p.act_general = act_general; p.act_alpha = act_alpha; p.act_limit = act_limit; p.up_offset = up_offset;
   p.staged = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * (epi == TC_EPI_RESIDUAL ? 4 : 2)) % 16 == 0) ? 1 : 0;
   return bn == 256 ? launch_tc<256>(ma, mw, p, n_sms, stream) : launch_tc<128>(ma, mw, p, n_sms, stream);
+}
+
+extern "C" int ie_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
+                               int epi, int bn, int n_sms, cudaStream_t stream) {
+  return ie_gemm_tcgen05_act(A, W, C, M, N, K, lda, ldw, ldc, epi, bn, n_sms, 0, 1.f, 0.f, 0.f, stream);
 }

@@ -145,33 +145,38 @@ extern "C" int ie_head_prepare(void* q, int q_stride, int q_heads, int q_hd, int
 #define HG_ROWS 8
 #define HG_THREADS 128
 
+// A block takes `groups` x HG_ROWS rows of one head: its threads are `groups` row groups of HG_THREADS / groups columns,
+// so that a narrow output (fewer columns than threads) still keeps every thread busy.
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(HG_THREADS) heads_gemm_kernel(const TX* __restrict__ x, int x_stride, int x_head,
                                                                 const TW* __restrict__ w, TO* __restrict__ out,
-                                                                int o_stride, int o_head, int M, int K, int N) {
-  extern __shared__ float xs[];          // [HG_ROWS][K]
+                                                                int o_stride, int o_head, int M, int K, int N, int groups) {
+  extern __shared__ float xs[];          // [groups * HG_ROWS][K]
   pdl_trigger();
   pdl_wait();
-  const int m0 = blockIdx.x * HG_ROWS, h = blockIdx.y;
-  const int rows = min(HG_ROWS, M - m0);
-  for (int i = threadIdx.x; i < HG_ROWS * K; i += HG_THREADS) {
+  const int block_rows = groups * HG_ROWS, cols = HG_THREADS / groups;
+  const int m0 = blockIdx.x * block_rows, h = blockIdx.y;
+  const int rows = min(block_rows, M - m0);
+  for (int i = threadIdx.x; i < block_rows * K; i += HG_THREADS) {
     const int r = i / K, k = i - r * K;
     xs[i] = r < rows ? to_f32(x[(size_t)(m0 + r) * x_stride + h * x_head + k]) : 0.f;
   }
   __syncthreads();
   const TW* wh = w + (size_t)h * K * N;
-  for (int j = threadIdx.x; j < N; j += HG_THREADS) {
+  const int rg = threadIdx.x / cols, r0 = rg * HG_ROWS;
+  const float* xg = xs + (size_t)r0 * K;
+  for (int j = threadIdx.x - rg * cols; j < N; j += cols) {
     float acc[HG_ROWS];
 #pragma unroll
     for (int r = 0; r < HG_ROWS; ++r) acc[r] = 0.f;
     for (int k = 0; k < K; ++k) {
       const float wv = to_f32(wh[(size_t)k * N + j]);
 #pragma unroll
-      for (int r = 0; r < HG_ROWS; ++r) acc[r] = fmaf(xs[r * K + k], wv, acc[r]);
+      for (int r = 0; r < HG_ROWS; ++r) acc[r] = fmaf(xg[r * K + k], wv, acc[r]);
     }
 #pragma unroll
     for (int r = 0; r < HG_ROWS; ++r)
-      if (r < rows) out[(size_t)(m0 + r) * o_stride + h * o_head + j] = from_f32<TO>(acc[r]);
+      if (r0 + r < rows) out[(size_t)(m0 + r0 + r) * o_stride + h * o_head + j] = from_f32<TO>(acc[r]);
   }
 }
 
@@ -179,9 +184,12 @@ extern "C" int ie_heads_gemm(const void* x, int x_dtype, int x_stride, int x_hea
                              int o_dtype, int o_stride, int o_head, int M, int H, int K, int N, cudaStream_t stream) {
   if (M <= 0 || H <= 0 || N <= 0) return IE_OK;
   if (K <= 0 || H > 65535) return IE_BAD_SIZE;
-  const size_t smem = sizeof(float) * HG_ROWS * (size_t)K;
+  // narrow outputs and enough rows: two or four row groups a block (a row's sum is the same whichever group forms it)
+  int groups = N <= 32 ? 4 : (N <= 64 ? 2 : 1);
+  while (groups > 1 && (M < groups * HG_ROWS || sizeof(float) * groups * HG_ROWS * (size_t)K > 96 * 1024)) groups >>= 1;
+  const size_t smem = sizeof(float) * groups * HG_ROWS * (size_t)K;
   if (smem > 96 * 1024) return IE_BAD_SIZE;
-  dim3 grid((M + HG_ROWS - 1) / HG_ROWS, H);
+  dim3 grid((M + groups * HG_ROWS - 1) / (groups * HG_ROWS), H);
 #define HG_GO(TX, TW, TO)                                                                                           \
   {                                                                                                                 \
     if (smem > 48 * 1024) {                                                                                         \
@@ -190,7 +198,7 @@ extern "C" int ie_heads_gemm(const void* x, int x_dtype, int x_stride, int x_hea
       if (e != cudaSuccess) return (int)e;                                                                          \
     }                                                                                                               \
     return launch_k(heads_gemm_kernel<TX, TW, TO>, grid, HG_THREADS, smem, stream, (const TX*)x, x_stride, x_head,  \
-                    (const TW*)w, (TO*)out, o_stride, o_head, M, K, N);                                             \
+                    (const TW*)w, (TO*)out, o_stride, o_head, M, K, N, groups);                                     \
   }
   if (x_dtype == IE_F32 && w_dtype == IE_F32 && o_dtype == IE_F32) HG_GO(float, float, float);
   if (x_dtype == IE_F32 && w_dtype == IE_BF16 && o_dtype == IE_F32) HG_GO(float, bf16, float);
@@ -232,6 +240,109 @@ __global__ void diff_combine_kernel(const T* __restrict__ maps, int maps_stride,
   }
 }
 
+// bfloat16 with an even head size up to 256 and rows that start on 4 bytes: a lane takes pairs, the head stays in registers
+__global__ void diff_combine_bf16_pairs_kernel(const bf16* __restrict__ maps, int maps_stride, const bf16* __restrict__ gate,
+                                               int gate_stride, bf16* __restrict__ out, int out_stride, int n_tokens,
+                                               int n_heads, int rep, int hd_v, float lambda, float eps, float out_mult) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= n_tokens * n_heads) return;
+  const int n = item / n_heads, h = item - n * n_heads;
+  const int g = h / rep, hg = h - g * rep;
+  const bf16* a1 = maps + (size_t)n * maps_stride + ((size_t)(g * 2 + 0) * rep + hg) * hd_v;
+  const bf16* a2 = maps + (size_t)n * maps_stride + ((size_t)(g * 2 + 1) * rep + hg) * hd_v;
+  float2 o[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = 2 * lane + 64 * i;
+    o[i] = make_float2(0.f, 0.f);
+    if (d < hd_v) {
+      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a1 + d));
+      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a2 + d));
+      o[i].x = fmaf(-lambda, y.x, x.x);
+      o[i].y = fmaf(-lambda, y.y, x.y);
+      ss = fmaf(o[i].x, o[i].x, ss);
+      ss = fmaf(o[i].y, o[i].y, ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = out_mult / sqrtf(ss / (float)hd_v + eps);
+  bf16* o_row = out + (size_t)n * out_stride + (size_t)h * hd_v;
+  const bf16* g_row = gate != nullptr ? gate + (size_t)n * gate_stride + (size_t)h * hd_v : nullptr;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = 2 * lane + 64 * i;
+    if (d < hd_v) {
+      float vx = o[i].x * inv, vy = o[i].y * inv;
+      if (g_row != nullptr) {
+        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g_row + d));
+        vx *= 1.f / (1.f + expf(-gg.x));
+        vy *= 1.f / (1.f + expf(-gg.y));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(o_row + d) = __floats2bfloat162_rn(vx, vy);
+    }
+  }
+}
+
+// bfloat16 with a head of 32, 64, 128 or 256 values and rows that start on 16 bytes: a lane takes eight values, the
+// hd_v / 8 lanes of a head sum their squares among themselves, a warp takes 32 / (hd_v / 8) heads
+__global__ void diff_combine_bf16_vec_kernel(const bf16* __restrict__ maps, int maps_stride, const bf16* __restrict__ gate,
+                                             int gate_stride, bf16* __restrict__ out, int out_stride, int n_tokens,
+                                             int n_heads, int rep, int hd_v, float lambda, float eps, float out_mult) {
+  pdl_trigger();
+  pdl_wait();
+  const int lanes = hd_v >> 3;                       // 4, 8, 16 or 32
+  const int per_warp = 32 / lanes;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lanes, l = lane - sub * lanes;
+  const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * per_warp + sub;
+  const bool live = item < (long long)n_tokens * n_heads;
+  const int n = live ? (int)(item / n_heads) : 0, h = live ? (int)(item - (long long)n * n_heads) : 0;
+  const int g = h / rep, hg = h - g * rep;
+  const int d = l * 8;
+  float o[8];
+  float ss = 0.f;
+  {
+    const uint4 x = *reinterpret_cast<const uint4*>(maps + (size_t)n * maps_stride + ((size_t)(g * 2 + 0) * rep + hg) * hd_v + d);
+    const uint4 y = *reinterpret_cast<const uint4*>(maps + (size_t)n * maps_stride + ((size_t)(g * 2 + 1) * rep + hg) * hd_v + d);
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+    const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 a = __bfloat1622float2(xp[t]), b = __bfloat1622float2(yp[t]);
+      o[2 * t] = fmaf(-lambda, b.x, a.x);
+      o[2 * t + 1] = fmaf(-lambda, b.y, a.y);
+      ss = fmaf(o[2 * t], o[2 * t], ss);
+      ss = fmaf(o[2 * t + 1], o[2 * t + 1], ss);
+    }
+  }
+  for (int s = 1; s < lanes; s <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  if (!live) return;
+  const float inv = out_mult / sqrtf(ss / (float)hd_v + eps);
+  float gs[8];
+  if (gate != nullptr) {
+    const uint4 gg = *reinterpret_cast<const uint4*>(gate + (size_t)n * gate_stride + (size_t)h * hd_v + d);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gg);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 a = __bfloat1622float2(gp[t]);
+      gs[2 * t] = 1.f / (1.f + expf(-a.x));
+      gs[2 * t + 1] = 1.f / (1.f + expf(-a.y));
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 8; ++t) gs[t] = 1.f;
+  }
+  uint4 r;
+  __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) rp[t] = __floats2bfloat162_rn(o[2 * t] * inv * gs[2 * t], o[2 * t + 1] * inv * gs[2 * t + 1]);
+  *reinterpret_cast<uint4*>(out + (size_t)n * out_stride + (size_t)h * hd_v + d) = r;
+}
+
 extern "C" int ie_diff_combine(const void* maps, int maps_stride, const void* gate, int gate_stride, void* out,
                                int out_stride, int n_tokens, int n_heads, int n_kv_heads, int hd_v, float lambda,
                                float eps, float out_mult, int act_dtype, cudaStream_t stream) {
@@ -240,6 +351,19 @@ extern "C" int ie_diff_combine(const void* maps, int maps_stride, const void* ga
   const int rep = n_heads / n_kv_heads;
   const int warps = 8;
   const unsigned blocks = (unsigned)(((size_t)n_tokens * n_heads + warps - 1) / warps);
+  if (act_dtype == IE_BF16 && (hd_v == 32 || hd_v == 64 || hd_v == 128 || hd_v == 256) && maps_stride % 8 == 0 &&
+      gate_stride % 8 == 0 && out_stride % 8 == 0 && (((uintptr_t)maps | (uintptr_t)gate | (uintptr_t)out) & 15) == 0) {
+    const int per_warp = 32 / (hd_v >> 3);
+    const size_t n_warps = ((size_t)n_tokens * n_heads + per_warp - 1) / per_warp;
+    return launch_k(diff_combine_bf16_vec_kernel, (unsigned)((n_warps + warps - 1) / warps), warps * 32, 0, stream,
+                    (const bf16*)maps, maps_stride, (const bf16*)gate, gate_stride, (bf16*)out, out_stride, n_tokens, n_heads,
+                    rep, hd_v, lambda, eps, out_mult);
+  }
+  if (act_dtype == IE_BF16 && hd_v % 2 == 0 && hd_v <= 256 && maps_stride % 2 == 0 && gate_stride % 2 == 0 && out_stride % 2 == 0 &&
+      (((uintptr_t)maps | (uintptr_t)gate | (uintptr_t)out) & 3) == 0)
+    return launch_k(diff_combine_bf16_pairs_kernel, blocks, warps * 32, 0, stream, (const bf16*)maps, maps_stride,
+                    (const bf16*)gate, gate_stride, (bf16*)out, out_stride, n_tokens, n_heads, rep, hd_v, lambda, eps,
+                    out_mult);
   if (act_dtype == IE_F32)
     return launch_k(diff_combine_kernel<float>, blocks, warps * 32, 0, stream, (const float*)maps, maps_stride,
                     (const float*)gate, gate_stride, (float*)out, out_stride, n_tokens, n_heads, rep, hd_v, lambda, eps,

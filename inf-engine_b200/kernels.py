@@ -732,6 +732,55 @@ def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before
                                     int(window or 0), float(scale), rows, _stream()), "attention_prefill_mma")
 
 
+_wide: dict[tuple, object] = {}
+
+
+def attention_wide_supports(q: torch.Tensor, out: torch.Tensor, head_dim: int, v_head_dim: int, v_row: int | None = None) -> bool:
+    """Whether the tensor-core kernel with float32 scores takes these operands: bfloat16, key and value head sizes
+    multiples of 16 up to 256, rows that start on 16 bytes."""
+    return (q.dtype is torch.bfloat16 and out.dtype is torch.bfloat16 and 0 < head_dim <= 256 and 0 < v_head_dim <= 256
+            and head_dim % 16 == 0 and v_head_dim % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 4 == 0 and (v_row or v_head_dim) % 8 == 0)
+
+
+def attention_wide_library(head_dim: int, v_head_dim: int):
+    """The tensor-core attention kernel with float32 scores built for one (key, value) head size; compiled when first
+    asked for."""
+    key = (int(head_dim), int(v_head_dim))
+    lib = _wide.get(key)
+    if lib is None:
+        defines = {"IE_AW_DK": key[0], "IE_AW_DV": key[1], **BUILD_DEFINES.get("attn_wide", {})}
+        lib = load_library(f"attn_wide_k{key[0]}_v{key[1]}", ["attention_wide.cu"], defines)
+        P, I, F = c_void_p, c_int, c_float
+        lib.ie_attention_wide.argtypes = [P] * 9 + [I] * 8 + [F, I, I, I, P]
+        lib.ie_attention_wide.restype = c_int
+        lib.ie_attention_wide_rows.restype = c_int
+        _wide[key] = lib
+        _apply_check_limits()
+    return lib
+
+
+ATTENTION_WIDE_ROWS = 64     # (token, head-in-group) pairs of a tile of the kernel below
+
+
+def attention_wide(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work, n_heads,
+                   n_kv_heads, head_dim, page_size, window, scale, v_head_dim: int | None = None, chunk: int = 0,
+                   n_v_heads: int | None = None, v_row: int | None = None) -> None:
+    """Causal paged attention of prompt portions on tensor cores with float32 scores, maxima and sums, the weights to
+    two bfloat16 terms: ``attention_general``'s options ``v_head_dim``, ``chunk``, ``n_v_heads`` and ``v_row`` and a
+    window, for bfloat16 operands whose head sizes are multiples of 16.  The work list cuts each request's (token,
+    head-in-group) pairs into tiles of ``ATTENTION_WIDE_ROWS``."""
+    dv = int(v_head_dim or head_dim)
+    assert attention_wide_supports(q, out, head_dim, dv, v_row) and kpool.dtype is torch.bfloat16 and vpool.dtype is torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    lib = attention_wide_library(head_dim, dv)
+    _check(lib.ie_attention_wide(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
+                                 _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0),
+                                 block_table.stride(0), n_work, n_heads, n_kv_heads, page_size, int(window or 0),
+                                 float(scale), int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
+           f"attention_wide(head_dim={head_dim}/{dv}, heads={n_heads}/{n_kv_heads})")
+
+
 def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim, biased: bool = False) -> int:
     # the same in both builds of a head size; ``biased`` only says which one to ask (the one the model has loaded)
     return int(attention_mma_library(head_dim, biased).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
@@ -1009,6 +1058,8 @@ def tcgen05_library():
         P, I = c_void_p, c_int
         lib.ie_gemm_tcgen05.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P]
         lib.ie_gemm_tcgen05.restype = c_int
+        lib.ie_gemm_tcgen05_act.argtypes = [c_void_p] * 3 + [c_int] * 10 + [c_float] * 3 + [c_void_p]
+        lib.ie_gemm_tcgen05_act.restype = c_int
         lib.ie_gemm_tcgen05_supports.argtypes = [I, I, I, I, I]
         lib.ie_gemm_tcgen05_supports.restype = c_int
         lib.ie_gemm_tcgen05_error.restype = c_int
@@ -1025,16 +1076,22 @@ def gemm_tcgen05_error() -> int:
     return int(tcgen05_library().ie_gemm_tcgen05_error())
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256) -> None:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256,
+                 act: tuple[float, float, float] | None = None) -> None:
     """c = a @ w^T on the fifth-generation tensor cores (TMA operands, accumulator in tensor memory).
 
     ``epi``: "bf16" store, "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating
-    gate/up and writes silu(gate)*up, half as wide.  ``bn``: tile width, 128 or 256."""
+    gate/up and writes silu(gate)*up, half as wide.  ``bn``: tile width, 128 or 256.  ``act`` = (alpha, limit, up_offset)
+    with "silu_mul": g' sigmoid(alpha g') (u' + up_offset) with g' = min(g, limit) and u' = clamp(u, -limit, limit)."""
     m, k = a.shape
     n = w.shape[0]
     assert a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
-    _check(tcgen05_library().ie_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0), c.stride(0),
-                                             _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
+    assert act is None or epi == "silu_mul"
+    alpha, limit, up_offset = act if act is not None else (1.0, 0.0, 0.0)
+    _check(tcgen05_library().ie_gemm_tcgen05_act(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0), c.stride(0),
+                                                 _EPI[epi], bn, sm_count(), 1 if act is not None else 0, float(alpha),
+                                                 float(limit), float(up_offset), _stream()),
+           f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
 
 
 # ------------------------------------------- prompt-portion attention on tcgen05 (head sizes 64 and 128)
@@ -1082,9 +1139,9 @@ def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, wo
 
 # ------------------------------------------------ a checks build: page ids, slots and token ids compared with limits
 # (the device has no sanitizer here: this is what stands in for one while debugging a cache manager or a new part)
-CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "delta_rule", "gated_delta")
+CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "attn_wide", "delta_rule", "gated_delta")
 CHECK_UNITS = ("elementwise", "rowwise", "sequence", "attention_general", "attention_mma", "attention_tcgen05",
-               "delta_rule", "gated_delta", "headwise", "gating")
+               "attention_wide", "delta_rule", "gated_delta", "headwise", "gating")
 CHECK_CODES = {1: "page id", 2: "cache slot", 3: "token id"}
 _check_limits: tuple[int, int, int] | None = None
 

@@ -66,11 +66,13 @@ class GatedMLP:
         s, ws, dt = self.spec, self.rt.ws, self.rt.act_dtype
         h = ws.take("ff_hidden", (n, s.intermediate), dt)
         w = self.gate_up.weight
-        if (self.plain_silu and dt is torch.bfloat16 and w.dtype is torch.bfloat16 and n >= self.TCGEN05_MIN_ROWS
+        if (dt is torch.bfloat16 and w.dtype is torch.bfloat16 and n >= self.TCGEN05_MIN_ROWS
                 and kernels.gemm_tcgen05_supports(n, 2 * s.intermediate, s.hidden, x.stride(0), w.stride(0))):
-            # gate/up on the tcgen05 tensor cores with silu(gate)*up in the epilogue: the [n, 2*intermediate]
+            # gate/up on the tcgen05 tensor cores with the gated activation in the epilogue: the [n, 2*intermediate]
             # matrix never goes to memory
-            kernels.gemm_tcgen05(x, w, h, "silu_mul")
+            act = None if self.plain_silu else \
+                ((s.act_alpha, s.act_limit, s.up_offset) if s.activation == "clamped_swish" else (1.0, float("inf"), s.up_offset))
+            kernels.gemm_tcgen05(x, w, h, "silu_mul", act=act)
         else:
             gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
             if self.plain_silu:

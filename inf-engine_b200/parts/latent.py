@@ -12,8 +12,10 @@ query heads over 2 x kv_heads key heads and kv_heads value heads.  The query row
 (``[kv head, map, head in group]``) so that the query heads of one key head lie side by side, as the attention
 kernels expect; a kernel then forms ``a1 - lambda a2``, norms it, and applies the output gate.
 
-Both run the float32 attention kernels (scores, maxima, weights and sums in float32 whatever the storage type): a block
-per (token, head) whose warps split the keys for requests that bring a few tokens, the tile kernel for prompt portions.
+Both keep scores, maxima, weights and sums in float32 whatever the storage type: a block per (token, head) whose
+warps split the keys for requests that bring a few tokens; for prompt portions the tensor-core kernel with float32
+scores (``kernels.attention_wide``: bfloat16 storage, head sizes that are multiples of 16) or else the float32 tile
+kernel on CUDA cores.
 """
 
 from __future__ import annotations
@@ -45,6 +47,12 @@ def attend_float32(q, out, kpool, vpool, ctx, kvctx, n_heads: int, n_kv_heads: i
                                max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
         if n_small == ctx.n_requests:
             return
+    if kpool.dtype is torch.bfloat16 and kernels.attention_wide_supports(q, out, head_dim, v_head_dim, v_row):
+        # prompt portions in bfloat16 storage: tensor cores, with float32 scores and the weights in two bfloat16 terms
+        work_req, work_pair0, n_work = ctx.attention_work(group, kernels.ATTENTION_WIDE_ROWS, max_rows if n_small else 0)
+        kernels.attention_wide(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, work_req, work_pair0,
+                               n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
+        return
     work_req, work_pair0, n_work = ctx.attention_work(group, 32, max_rows if n_small else 0)
     kernels.attention_general(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, work_req, work_pair0,
                               n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)

@@ -77,15 +77,22 @@ FVX_C = _model(131, 100, 1e-5, 0.5, [
     _diff(5, 1, 10, 6, 0.35, 0.1, None, 16, None),
     _gru(35, _mlp(12, 3.0)),
 ], loop=(0, 3, 2))
+# head sizes that are multiples of 16, which the tensor-core attention of prompt portions takes: two maps of 16 over
+# values of 32 in chunks of 40, a compressed row of 32 + 16; the attention layers run twice
+FVX_W = _model(300, 128, 1e-5, 4.0, [
+    _diff(4, 2, 16, 32, 0.25, 0.3, _rot(1000.0, 8), 40, _mlp(96, 1.5)),
+    _latent(3, 16, 16, 16, 32, 0.2, _rot(400.0, 16, (2.0, 32, 8.0, 1.0)), None, _mlp(64, 2.0)),
+    _gru(80, None),
+], loop=(0, 2, 2))
 # one mechanism each
 FVX_LAT = _model(120, 48, 1e-5, 2.0, [_latent(4, 12, 4, 8, 16, 0.3, _rot(200.0, 4, (4.0, 32, 8.0, 1.0)), None, None)])
 FVX_DIFF = _model(120, 48, 1e-5, 2.0, [_diff(6, 3, 12, 8, 0.3, 0.4, _rot(1000.0, 6), 19, None)])
 FVX_GRU = _model(120, 48, 1e-5, 2.0, [_gru(56, None)])
 FVX_FF = _model(120, 48, 1e-6, 2.0, [_gru(16, _mlp(28, 0.8))])
 
-MODELS = {"fvx_a": FVX_A, "fvx_b": FVX_B, "fvx_c": FVX_C, "fvx_lat": FVX_LAT, "fvx_diff": FVX_DIFF, "fvx_gru": FVX_GRU,
+MODELS = {"fvx_a": FVX_A, "fvx_b": FVX_B, "fvx_c": FVX_C, "fvx_w": FVX_W, "fvx_lat": FVX_LAT, "fvx_diff": FVX_DIFF, "fvx_gru": FVX_GRU,
           "fvx_ff": FVX_FF}
-SEEDS = {"fvx_a": 41, "fvx_b": 42, "fvx_c": 43, "fvx_lat": 44, "fvx_diff": 45, "fvx_gru": 46, "fvx_ff": 47}
+SEEDS = {"fvx_w": 48, "fvx_a": 41, "fvx_b": 42, "fvx_c": 43, "fvx_lat": 44, "fvx_diff": 45, "fvx_gru": 46, "fvx_ff": 47}
 
 
 def lively(tensors: dict) -> None:

@@ -176,7 +176,8 @@ def test_heads_gemm_kernel(dtype, m, heads, kd, nd):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, kv, dv, gated", [(4, 2, 24, True), (3, 3, 12, False), (5, 1, 6, True), (2, 1, 80, True)])
+@pytest.mark.parametrize("heads, kv, dv, gated", [(4, 2, 24, True), (3, 3, 12, False), (5, 1, 6, True), (2, 1, 80, True),
+                                                  (6, 2, 32, True), (5, 5, 64, True), (3, 1, 128, False), (2, 2, 256, True)])
 def test_diff_combine_kernel(dtype, heads, kv, dv, gated):
     dt = TORCH[dtype]
     g = torch.Generator().manual_seed(6)
@@ -222,6 +223,30 @@ def test_gates_scale_and_activation_kernels(dtype):
         assert float((gg > 1.3).float().mean()) > 0.1 and float((uu < -1.3).float().mean()) > 0.1
         k().glu_act(gu.to(DEV), out, "silu", interleaved=inter)
         assert close(out, gg * torch.sigmoid(gg) * uu, dtype)
+
+
+@pytest.mark.parametrize("M, N, K, bn", [(200, 320, 128, 128), (384, 1024, 256, 256), (129, 96, 64, 256)])
+def test_clamped_activation_in_the_epilogue_of_the_tensor_core_product(M, N, K, bn):
+    """Gate and up as alternating weight rows; both branches reach their limits; full tiles and edge tiles."""
+    g = torch.Generator().manual_seed(M + N)
+    bf = torch.bfloat16
+    a = torch.randn(M, K, generator=g).to(bf)
+    w = (torch.randn(N, K, generator=g) * 0.25).to(bf)
+    ref = a.double() @ w.double().T
+    gg, uu = ref[:, 0::2], ref[:, 1::2]
+    limit, alpha, off = 1.7, 1.702, 1.0
+    assert float((gg > limit).float().mean()) > 0.1 and float((uu < -limit).float().mean()) > 0.1
+    gc = gg.clamp(max=limit)
+    want = gc * torch.sigmoid(alpha * gc) * (uu.clamp(-limit, limit) + off)
+    h = torch.full((M, N // 2), float("nan"), device=DEV, dtype=bf)
+    k().gemm_tcgen05(a.to(DEV), w.to(DEV), h, "silu_mul", bn, act=(alpha, limit, off))
+    assert float((h.double().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+    # no clamp at all: a limit of infinity, the plain activation with an offset
+    want = gg * torch.sigmoid(gg) * (uu + 0.5)
+    k().gemm_tcgen05(a.to(DEV), w.to(DEV), h, "silu_mul", bn, act=(1.0, float("inf"), 0.5))
+    assert float((h.double().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+    torch.cuda.synchronize()
+    assert k().gemm_tcgen05_error() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -368,6 +393,100 @@ def test_a_key_stands_out_only_inside_the_chunk(dtype, rows_kernel, shape):
         assert near_hot == sees, (p, sees)
 
 
+@pytest.mark.parametrize("dk, dv, n_heads, n_k, n_v, in_keys, chunk, window, ps", [
+    (64, 128, 8, 4, 2, False, 37, None, 16),      # two key heads a value head, values twice the keys
+    (16, 16, 3, 1, 1, False, None, None, 8),      # the smallest sizes, three heads over one
+    (48, 80, 6, 2, 1, False, 50, None, 16),
+    (256, 192, 5, 1, 1, True, None, None, 16),    # values inside the key rows; the short key tile
+    (80, 48, 7, 1, 1, True, 21, None, 8),
+    (32, 16, 4, 4, 4, False, None, 29, 8),        # a window
+    (144, 112, 2, 2, 2, False, 64, None, 32),
+    (256, 256, 2, 1, 1, False, None, None, 16),
+])
+def test_tensor_core_attention_with_float32_scores(dk, dv, n_heads, n_k, n_v, in_keys, chunk, window, ps):
+    """The tensor-core kernel for prompt portions against attention written out in float64: two requests of unequal
+    length in one step (one continues after 45 cached tokens, a count that is no multiple of a page or a tile), pages
+    in random order, unwritten slots poisoned, pages before the visible keys released, a key that dominates every
+    score of its request so that a mask that is one key off shows, rows of q and out with columns beside the heads."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(dk * 7 + dv)
+    lens, before = [131, 70], [45, 0]
+    group = n_heads // n_k
+    scale = 0.4 / math.sqrt(dk)
+    qs, outs, tables, wants = [], [], [], []
+    n_pages_each = [-(-(b + L) // ps) for L, b in zip(lens, before)]
+    total_pages = sum(n_pages_each) + 3
+    perm = torch.randperm(total_pages, generator=g)
+    kpool = torch.full((total_pages, n_k, ps, dk), float("nan"), dtype=dt)
+    vpool = kpool if in_keys else torch.full((total_pages, n_v, ps, dv), float("nan"), dtype=dt)
+    at = 0
+    for r, (L, b) in enumerate(zip(lens, before)):
+        T = b + L
+        kk = torch.randn(T, n_k, dk, generator=g)
+        hot = b + 9
+        direction = torch.randn(dk, generator=g)
+        if in_keys:
+            direction[:dv] = 0
+        direction /= direction.norm()
+        kk[hot] += 12 * math.sqrt(dk) * direction
+        q = torch.randn(L, n_heads, dk, generator=g) + 2 * direction
+        kk, q = kk.to(dt), q.to(dt)
+        v = kk[:, :, :dv].clone() if in_keys else torch.randn(T, n_v, dv, generator=g).to(dt)
+        pages = perm[at:at + n_pages_each[r]]
+        at += n_pages_each[r]
+        for t in range(T):
+            kpool[pages[t // ps], :, t % ps] = kk[t]
+            if not in_keys:
+                vpool[pages[t // ps], :, t % ps] = v[t]
+        table = torch.full((max(n_pages_each),), -1, dtype=torch.int32)
+        table[:len(pages)] = pages.to(torch.int32)
+        first_seen = 0
+        if chunk:
+            first_seen = (b // chunk) * chunk
+        if window:
+            first_seen = max(first_seen, b - window + 1)
+        table[:first_seen // ps] = -1              # nothing before the first query's first visible key is held
+        tables.append(table)
+        want = torch.zeros(L, n_heads, dv, dtype=torch.float64)
+        for t in range(L):
+            p_ = b + t
+            lo = max((p_ // chunk) * chunk if chunk else 0, p_ - window + 1 if window else 0)
+            for h in range(n_heads):
+                c = h // group
+                sc = (kk.double()[lo:p_ + 1, c] @ q.double()[t, h]) * scale
+                want[t, h] = torch.softmax(sc, 0) @ v.double()[lo:p_ + 1, c // (n_k // n_v)]
+        wants.append(want)
+        qs.append(q.reshape(L, -1))
+    n = sum(lens)
+    qrows = torch.zeros(n, n_heads * dk + 8, dtype=dt)
+    qrows[:, :n_heads * dk] = torch.cat(qs)
+    out = torch.full((n, n_heads * dv + 2), 5.0, dtype=dt, device=DEV)
+    rows = k().ATTENTION_WIDE_ROWS
+    work = [(r, p0) for r, L in enumerate(lens) for p0 in range(0, L * group, rows)]
+    kp = kpool.to(DEV)
+    vp = kp if in_keys else vpool.to(DEV)
+    qd = qrows.to(DEV)
+    assert k().attention_wide_supports(qd[:, :n_heads * dk], out[:, :n_heads * dv], dk, dv, dk if in_keys else None)
+    k().attention_wide(qd[:, :n_heads * dk], out[:, :n_heads * dv], kp, vp, torch.stack(tables).to(DEV), dev_i32([0, lens[0], n]),
+                       dev_i32(before), dev_i32([w_[0] for w_ in work]), dev_i32([w_[1] for w_ in work]), len(work), n_heads, n_k,
+                       dk, ps, window, scale, v_head_dim=dv, chunk=chunk or 0, n_v_heads=n_v, v_row=dk if in_keys else None)
+    got = out[:, :n_heads * dv].double().cpu().reshape(n, n_heads, dv)
+    assert torch.isfinite(got).all() and bool((out[:, n_heads * dv:] == 5.0).all())
+    want = torch.cat(wants)
+    err = (got - want).abs().amax(dim=(1, 2))
+    bound = 1.2e-2 * want.abs().amax(dim=(1, 2)).clamp(min=0.05)        # the output's own bfloat16 rounding and a little
+    bad = torch.nonzero(err > bound).flatten().tolist()
+    assert not bad, (bad[:8], float(err.max()))
+    # and the general kernel agrees to the output's rounding
+    out2 = torch.empty(n, n_heads * dv, dtype=dt, device=DEV)
+    work32 = [(r, p0) for r, L in enumerate(lens) for p0 in range(0, L * group, 32)]
+    k().attention_general(qd[:, :n_heads * dk], out2, kp, vp, torch.stack(tables).to(DEV), dev_i32([0, lens[0], n]), dev_i32(before),
+                          dev_i32([w_[0] for w_ in work32]), dev_i32([w_[1] for w_ in work32]), len(work32), n_heads, n_k, dk, ps,
+                          window, scale, v_head_dim=dv, chunk=chunk or 0, n_v_heads=n_v, v_row=dk if in_keys else None)
+    diff = (out2.double().cpu().reshape(n, n_heads, dv) - got).abs().amax(dim=(1, 2))
+    assert bool((diff <= bound).all()), float(diff.max())
+
+
 # =============================================================== whole models
 def load(folder, dtype, page_size=16, n_pages=64, max_requests=4, **kw):
     from inf_engine_b200 import ModelRunner
@@ -402,7 +521,7 @@ def steady_tokens(cfg, w, n: int, seed: int) -> list[int]:
     raise AssertionError("no well-conditioned sequence in 50 seeds")
 
 
-LENGTH = {"fvx_a": 97, "fvx_b": 70, "fvx_c": 131, "fvx_lat": 60, "fvx_diff": 75, "fvx_gru": 50, "fvx_ff": 41}
+LENGTH = {"fvx_a": 97, "fvx_b": 70, "fvx_c": 131, "fvx_w": 150, "fvx_lat": 60, "fvx_diff": 75, "fvx_gru": 50, "fvx_ff": 41}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -423,7 +542,7 @@ def test_whole_prompt_decoding_and_portions_agree_with_the_plain_model(tmp_path,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["fvx_a", "fvx_b", "fvx_c"])
+@pytest.mark.parametrize("name", ["fvx_a", "fvx_b", "fvx_c", "fvx_w"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(tmp_path, name, dtype):
     """Seven requests, at most three live, portions of some beside decoded tokens of others, some left out of a step;
     the pool holds exactly what the fullest moment needs and free pages are filled with NaN."""
