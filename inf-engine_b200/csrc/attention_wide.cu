@@ -50,6 +50,14 @@ struct WideParams {
   int v_row;       // elements between two value rows of the value pool
   int alias;       // the values are the first DV dimensions of the key rows: the key tile is the value tile
   float scale_log2;
+  // without a work list (work_req null): block x is tile x % tiles of request x / tiles, and only requests that bring
+  // at most max_rows (token, head-in-group) pairs take part (decode tokens; the others are a work list's)
+  int tiles, max_rows;
+  // n_splits > 1: block z takes the keys [first + z * split_keys, first + (z + 1) * split_keys) of its tile's range
+  // (split_keys a multiple of the key tile) and leaves sums, maxima and unnormalised outputs for the merge kernel
+  int n_splits, split_keys;
+  float* part_o;   // [blocks x, key heads, splits, BM, DV]
+  float* part_ml;  // [blocks x, key heads, splits, BM, 2]
 };
 
 __device__ __forceinline__ void cp16(void* dst, const void* src) {
@@ -123,13 +131,14 @@ __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
   bf16* Kbuf = Qs + BM * LDK;                     // [2][BN][LDK]
   bf16* Vbuf = Kbuf + 2 * BN * LDK;               // [2][BN][LDV] (unused when the values are in the keys)
 
-  const int r_id = p.work_req[blockIdx.x];
-  const int pair0 = p.work_pair0[blockIdx.x];
+  const int r_id = p.work_req != nullptr ? p.work_req[blockIdx.x] : (int)blockIdx.x / p.tiles;
+  const int pair0 = p.work_req != nullptr ? p.work_pair0[blockIdx.x] : ((int)blockIdx.x % p.tiles) * BM;
   const int c = blockIdx.y;
   const int group = p.n_heads / p.n_kv_heads;
   const int cv = c / (p.n_kv_heads / p.n_v_heads);
   const int q0 = p.q_start[r_id];
   const int n_pairs = (p.q_start[r_id + 1] - q0) * group;
+  if (p.work_req == nullptr && (n_pairs > p.max_rows || pair0 >= n_pairs)) return;
   const int ctx = p.ctx_before[r_id];
   const int* table = p.block_table + (size_t)r_id * p.table_stride;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
@@ -178,11 +187,16 @@ __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int ldv = p.alias ? LDK : LDV;
 
-  load_tile(p, Kbuf, Vbuf, key_begin, key_end, table, c, cv, tid);
+  int k_lo = key_begin, k_hi = key_end;
+  if (p.n_splits > 1) {
+    k_lo = key_begin + (int)blockIdx.z * p.split_keys;
+    k_hi = min(key_end, k_lo + p.split_keys);
+  }
+  if (k_lo < k_hi) load_tile(p, Kbuf, Vbuf, k_lo, key_end, table, c, cv, tid);
   cp_commit();
   int buf = 0;
-  for (int kt = key_begin; kt < key_end; kt += BN, buf ^= 1) {
-    const bool more = kt + BN < key_end;
+  for (int kt = k_lo; kt < k_hi; kt += BN, buf ^= 1) {
+    const bool more = kt + BN < k_hi;
     if (more) {
       load_tile(p, Kbuf + (buf ^ 1) * BN * LDK, Vbuf + (buf ^ 1) * BN * LDV, kt + BN, key_end, table, c, cv, tid);
       cp_commit();
@@ -274,6 +288,26 @@ __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
   }
   cp_wait<0>();
 
+  if (p.n_splits > 1) {
+    const size_t part = ((size_t)blockIdx.x * p.n_kv_heads + c) * p.n_splits + blockIdx.z;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float l = l_run[h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (pr_[h] >= n_pairs) continue;
+      const size_t row = part * BM + warp * 16 + g + 8 * h;
+      if (t4 == 0) {
+        p.part_ml[row * 2] = m_run[h];
+        p.part_ml[row * 2 + 1] = l;
+      }
+      float* dst = p.part_o + row * DV + 2 * t4;
+#pragma unroll
+      for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+    }
+    return;
+  }
+
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float l = l_run[h];
@@ -289,18 +323,53 @@ __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
   }
 }
 
+// the splits of a tile become its output rows: out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m = max_s m_s
+__global__ void __launch_bounds__(THREADS) attention_wide_merge_kernel(WideParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int r_id = (int)blockIdx.x / p.tiles, pair0 = ((int)blockIdx.x % p.tiles) * BM;
+  const int c = blockIdx.y;
+  const int group = p.n_heads / p.n_kv_heads;
+  const int q0 = p.q_start[r_id];
+  const int n_pairs = (p.q_start[r_id + 1] - q0) * group;
+  if (n_pairs > p.max_rows || pair0 >= n_pairs) return;
+  const int rows = min(BM, n_pairs - pair0);
+  const size_t part0 = ((size_t)blockIdx.x * p.n_kv_heads + c) * p.n_splits;
+  for (int idx = threadIdx.x; idx < rows * (DV / 2); idx += THREADS) {
+    const int r = idx / (DV / 2), d = (idx - r * (DV / 2)) * 2;
+    float m_all = -INFINITY;
+    for (int s = 0; s < p.n_splits; ++s) m_all = fmaxf(m_all, p.part_ml[((part0 + s) * BM + r) * 2]);
+    float l_all = 0.f, ox = 0.f, oy = 0.f;
+    if (m_all != -INFINITY) {
+      for (int s = 0; s < p.n_splits; ++s) {
+        const size_t row = (part0 + s) * BM + r;
+        const float m_s = p.part_ml[row * 2];
+        if (m_s == -INFINITY) continue;
+        const float w = exp2f(m_s - m_all);
+        l_all = fmaf(p.part_ml[row * 2 + 1], w, l_all);
+        const float2 v = *reinterpret_cast<const float2*>(p.part_o + row * DV + d);
+        ox = fmaf(v.x, w, ox);
+        oy = fmaf(v.y, w, oy);
+      }
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    const int pr = pair0 + r;
+    const int t = pr / group, j = pr - t * group;
+    bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + (size_t)(c * group + j) * DV + d;
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(ox * inv, oy * inv);
+  }
+}
+
 }  // namespace
 
 extern "C" int ie_attention_wide_key_dim() { return DK; }
 extern "C" int ie_attention_wide_value_dim() { return DV; }
 extern "C" int ie_attention_wide_rows() { return BM; }
+extern "C" int ie_attention_wide_keys() { return BN; }
 
-extern "C" int ie_attention_wide(const void* q, void* out, const void* kpool, const void* vpool, const int* block_table,
-                                 const int* q_start, const int* ctx_before, const int* work_req, const int* work_pair0,
-                                 int q_stride, int out_stride, int table_stride, int n_work, int n_heads, int n_kv_heads,
-                                 int page_size, int window, float scale, int chunk, int n_v_heads, int v_row,
-                                 cudaStream_t stream) {
-  if (n_work <= 0) return IE_OK;
+static int wide_params(WideParams& p, const void* q, void* out, const void* kpool, const void* vpool, const int* block_table,
+                       const int* q_start, const int* ctx_before, int q_stride, int out_stride, int table_stride, int n_heads,
+                       int n_kv_heads, int page_size, int window, float scale, int chunk, int n_v_heads, int v_row) {
   if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || window < 0 || chunk < 0) return IE_BAD_SIZE;
   if (n_v_heads <= 0) n_v_heads = n_kv_heads;
   if (v_row <= 0) v_row = DV;
@@ -309,18 +378,72 @@ extern "C" int ie_attention_wide(const void* q, void* out, const void* kpool, co
   if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15) || ((uintptr_t)out & 3) || (q_stride & 7) ||
       (out_stride & 1) || (v_row & 7))
     return IE_BAD_ALIGN;
-  WideParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kpool = (const bf16*)kpool; p.vpool = (const bf16*)vpool;
-  p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = work_req; p.work_pair0 = work_pair0;
+  p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = nullptr; p.work_pair0 = nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window; p.chunk = chunk;
   p.n_v_heads = n_v_heads; p.v_row = v_row;
   p.alias = (vpool == kpool && v_row == DK && n_v_heads == n_kv_heads && DV <= DK) ? 1 : 0;
   p.scale_log2 = scale * LOG2E;
-  const size_t smem = sizeof(bf16) * ((size_t)BM * LDK + 2 * (size_t)BN * LDK + (p.alias ? 0 : 2 * (size_t)BN * LDV));
+  p.tiles = 1; p.max_rows = 0; p.n_splits = 1; p.split_keys = 0; p.part_o = nullptr; p.part_ml = nullptr;
+  return IE_OK;
+}
+
+static size_t wide_smem(const WideParams& p) {
+  return sizeof(bf16) * ((size_t)BM * LDK + 2 * (size_t)BN * LDK + (p.alias ? 0 : 2 * (size_t)BN * LDV));
+}
+
+extern "C" int ie_attention_wide(const void* q, void* out, const void* kpool, const void* vpool, const int* block_table,
+                                 const int* q_start, const int* ctx_before, const int* work_req, const int* work_pair0,
+                                 int q_stride, int out_stride, int table_stride, int n_work, int n_heads, int n_kv_heads,
+                                 int page_size, int window, float scale, int chunk, int n_v_heads, int v_row,
+                                 cudaStream_t stream) {
+  if (n_work <= 0) return IE_OK;
+  if (work_req == nullptr || work_pair0 == nullptr) return IE_BAD_SIZE;
+  WideParams p;
+  const int rc = wide_params(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride,
+                             n_heads, n_kv_heads, page_size, window, scale, chunk, n_v_heads, v_row);
+  if (rc != IE_OK) return rc;
+  p.work_req = work_req; p.work_pair0 = work_pair0;
+  const size_t smem = wide_smem(p);
   cudaError_t e = cudaFuncSetAttribute(attention_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   return launch_k(attention_wide_kernel, dim3(n_work, n_kv_heads), THREADS, smem, stream, p);
+}
+
+// floats of scratch that ie_attention_wide_small needs
+extern "C" long long ie_attention_wide_small_scratch(int n_requests, int max_rows, int n_kv_heads, int n_splits) {
+  const long long tiles = (max_rows + BM - 1) / BM;
+  return n_splits > 1 ? (long long)n_requests * tiles * n_kv_heads * n_splits * BM * (DV + 2) : 0;
+}
+
+// The requests of the step that bring at most max_rows (token, head-in-group) pairs (decode tokens, as a rule), without
+// a work list: every such request's keys are cut into n_splits runs of split_keys keys (a multiple of the key tile;
+// n_splits * split_keys covers the longest visible run, counted from the tile boundary below its first key), a block a
+// run, and a second kernel merges the runs.  Rows of requests that bring more are left untouched.
+extern "C" int ie_attention_wide_small(const void* q, void* out, const void* kpool, const void* vpool, const int* block_table,
+                                       const int* q_start, const int* ctx_before, int q_stride, int out_stride,
+                                       int table_stride, int n_requests, int max_rows, int n_heads, int n_kv_heads,
+                                       int page_size, int window, float scale, int chunk, int n_v_heads, int v_row,
+                                       int n_splits, int split_keys, float* scratch, cudaStream_t stream) {
+  if (n_requests <= 0) return IE_OK;
+  if (max_rows <= 0 || n_splits <= 0 || n_splits > 65535) return IE_BAD_SIZE;
+  if (n_splits > 1 && (split_keys <= 0 || split_keys % BN || scratch == nullptr)) return IE_BAD_SIZE;
+  WideParams p;
+  const int rc = wide_params(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride,
+                             n_heads, n_kv_heads, page_size, window, scale, chunk, n_v_heads, v_row);
+  if (rc != IE_OK) return rc;
+  p.tiles = (max_rows + BM - 1) / BM; p.max_rows = max_rows; p.n_splits = n_splits; p.split_keys = split_keys;
+  const size_t n_parts = (size_t)n_requests * p.tiles * n_kv_heads * n_splits;
+  p.part_o = scratch;
+  p.part_ml = scratch != nullptr ? scratch + n_parts * BM * DV : nullptr;
+  const size_t smem = wide_smem(p);
+  cudaError_t e = cudaFuncSetAttribute(attention_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const dim3 grid(n_requests * p.tiles, n_kv_heads, n_splits);
+  int st = launch_k(attention_wide_kernel, grid, THREADS, smem, stream, p);
+  if (st != IE_OK || n_splits == 1) return st;
+  return launch_k(attention_wide_merge_kernel, dim3(grid.x, grid.y), THREADS, 0, stream, p);
 }
 
 IE_CHECK_API(attention_wide)

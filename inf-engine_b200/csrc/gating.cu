@@ -189,12 +189,126 @@ __global__ void mingru_scan_kernel(const T* __restrict__ z_pre, const T* __restr
   if (write_state) state[(size_t)slot * width + c] = S;
 }
 
+// The same recurrence for requests that bring many tokens (prompt portions).  The recurrence is linear in the state,
+// S_t = (1 - z_t) S_(t-1) + z_t c_t, so a run of tokens maps the state it starts from to A S + B with A = prod (1 - z_t)
+// and B the run's result from a zero state.  A block takes MGS_CH channels of one request and cuts its tokens into
+// MGS_SEG runs, a thread a (channel, run): pass one forms every run's (A, B), the first run's threads then carry the
+// state through the MGS_SEG pairs, pass two repeats every run from its true starting state and writes the outputs.
+// Twice the arithmetic and reads (the second time from cache) for a dependent chain of T / MGS_SEG + MGS_SEG steps.
+#define MGS_CH 32
+#define MGS_SEG 16
+
+template <typename T, typename TB>
+__global__ void __launch_bounds__(MGS_CH * MGS_SEG) mingru_scan_segments_kernel(
+    const T* __restrict__ z_pre, const T* __restrict__ u_pre, int zu_stride, const T* __restrict__ g_pre, int g_stride,
+    const TB* __restrict__ z_bias, const TB* __restrict__ u_bias, float* __restrict__ state, T* __restrict__ out,
+    int out_stride, const int* __restrict__ q_start, const int* __restrict__ slots, int width, int write_state) {
+  __shared__ float sA[MGS_SEG][MGS_CH], sB[MGS_SEG][MGS_CH];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int slot = IE_SLOT(slots[r]);
+  if (slot < 0) return;                              // (the whole block)
+  const int cx = threadIdx.x, sg = threadIdx.y;
+  const int c = blockIdx.x * MGS_CH + cx;
+  const bool live = c < width;
+  const int cc = live ? c : width - 1;
+  const int t0 = q_start[r], t1 = q_start[r + 1];
+  const int seg_len = (t1 - t0 + MGS_SEG - 1) / MGS_SEG;
+  const int a = min(t1, t0 + sg * seg_len), b = min(t1, a + seg_len);
+  const float bz = z_bias != nullptr ? to_f32(z_bias[cc]) : 0.f, bu = u_bias != nullptr ? to_f32(u_bias[cc]) : 0.f;
+  float A = 1.f, B = 0.f;
+  for (int t = a; t < b; t += MG_UNROLL) {
+    float zp[MG_UNROLL], up[MG_UNROLL];
+#pragma unroll
+    for (int i = 0; i < MG_UNROLL; ++i) {
+      const size_t row = (size_t)(t + i < b ? t + i : t);
+      zp[i] = to_f32(z_pre[row * zu_stride + cc]);
+      up[i] = to_f32(u_pre[row * zu_stride + cc]);
+    }
+#pragma unroll
+    for (int i = 0; i < MG_UNROLL; ++i) {
+      if (t + i < b) {
+        const float z = sigmoid_f(zp[i] + bz);
+        const float u = up[i] + bu;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        A *= 1.f - z;
+        B = fmaf(z, cand - B, B);
+      }
+    }
+  }
+  sA[sg][cx] = A;
+  sB[sg][cx] = B;
+  __syncthreads();
+  if (sg == 0) {
+    float S = state[(size_t)slot * width + cc];
+    for (int k = 0; k < MGS_SEG; ++k) {
+      const float a_k = sA[k][cx], b_k = sB[k][cx];
+      sA[k][cx] = S;                                 // the state that run k starts from
+      S = fmaf(a_k, S, b_k);
+    }
+    if (write_state && live) state[(size_t)slot * width + c] = S;
+  }
+  __syncthreads();
+  float S = sA[sg][cx];
+  for (int t = a; t < b; t += MG_UNROLL) {
+    float zp[MG_UNROLL], up[MG_UNROLL], gp[MG_UNROLL];
+#pragma unroll
+    for (int i = 0; i < MG_UNROLL; ++i) {
+      const size_t row = (size_t)(t + i < b ? t + i : t);
+      zp[i] = to_f32(z_pre[row * zu_stride + cc]);
+      up[i] = to_f32(u_pre[row * zu_stride + cc]);
+      gp[i] = to_f32(g_pre[row * g_stride + cc]);
+    }
+#pragma unroll
+    for (int i = 0; i < MG_UNROLL; ++i) {
+      if (t + i < b) {
+        const float z = sigmoid_f(zp[i] + bz);
+        const float u = up[i] + bu;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        S = fmaf(z, cand - S, S);
+        if (live) out[(size_t)(t + i) * out_stride + c] = from_f32<T>(S * (gp[i] * sigmoid_f(gp[i])));
+      }
+    }
+  }
+}
+
+// max_q_len: the most tokens a request of the step brings, if the host knows (0: it does not); from MGS_MIN_TOKENS on the
+// kernel that cuts each request's tokens into runs is launched
+#define MGS_MIN_TOKENS 64
+
+extern "C" int ie_mingru_scan_hint(const void* z_pre, const void* u_pre, int zu_stride, const void* g_pre, int g_stride,
+                                   const void* z_bias, const void* u_bias, int bias_dtype, float* state, void* out,
+                                   int out_stride, const int* q_start, const int* slots, int n_requests, int width,
+                                   int write_state, int act_dtype, int max_q_len, cudaStream_t stream);
+
 extern "C" int ie_mingru_scan(const void* z_pre, const void* u_pre, int zu_stride, const void* g_pre, int g_stride,
                               const void* z_bias, const void* u_bias, int bias_dtype, float* state, void* out,
                               int out_stride, const int* q_start, const int* slots, int n_requests, int width,
                               int write_state, int act_dtype, cudaStream_t stream) {
+  return ie_mingru_scan_hint(z_pre, u_pre, zu_stride, g_pre, g_stride, z_bias, u_bias, bias_dtype, state, out, out_stride,
+                             q_start, slots, n_requests, width, write_state, act_dtype, 0, stream);
+}
+
+extern "C" int ie_mingru_scan_hint(const void* z_pre, const void* u_pre, int zu_stride, const void* g_pre, int g_stride,
+                              const void* z_bias, const void* u_bias, int bias_dtype, float* state, void* out,
+                                   int out_stride, const int* q_start, const int* slots, int n_requests, int width,
+                                   int write_state, int act_dtype, int max_q_len, cudaStream_t stream) {
   if (n_requests <= 0 || width <= 0) return IE_OK;
   if (n_requests > 65535) return IE_BAD_SIZE;
+  if (max_q_len >= MGS_MIN_TOKENS) {
+    const dim3 sgrid((width + MGS_CH - 1) / MGS_CH, n_requests), sblock(MGS_CH, MGS_SEG);
+#define MGS_GO(T, TB)                                                                                                    \
+  return launch_k(mingru_scan_segments_kernel<T, TB>, sgrid, sblock, 0, stream, (const T*)z_pre, (const T*)u_pre, zu_stride, \
+                  (const T*)g_pre, g_stride, (const TB*)z_bias, (const TB*)u_bias, state, (T*)out, out_stride, q_start,     \
+                  slots, width, write_state)
+    if (act_dtype == IE_F32 && bias_dtype == IE_F32) MGS_GO(float, float);
+    if (act_dtype == IE_F32 && bias_dtype == IE_BF16) MGS_GO(float, bf16);
+    if (act_dtype == IE_BF16 && bias_dtype == IE_F32) MGS_GO(bf16, float);
+    if (act_dtype == IE_BF16 && bias_dtype == IE_BF16) MGS_GO(bf16, bf16);
+#undef MGS_GO
+    return IE_BAD_DTYPE;
+  }
   const int threads = 64;
   dim3 grid((width + threads - 1) / threads, n_requests);
 #define MG_GO(T, TB)                                                                                              \

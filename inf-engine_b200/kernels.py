@@ -108,6 +108,7 @@ def core():
         lib.ie_scale_rows.argtypes = [P, P, F, I, I, P]
         lib.ie_glu_act.argtypes = [P, P, I, I, I, I, I, F, F, F, I, P]
         lib.ie_mingru_scan.argtypes = [P, P, I, P, I, P, P, I, P, P, I, P, P, I, I, I, I, P]
+        lib.ie_mingru_scan_hint.argtypes = [P, P, I, P, I, P, P, I, P, P, I, P, P, I, I, I, I, I, P]
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
         lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
         lib.ie_sample.argtypes = [P, P, P, I, I, L, P]
@@ -118,7 +119,7 @@ def core():
                      "ie_causal_conv", "ie_linear_recurrence", "ie_rownorm_rotate_write", "ie_moe_route", "ie_moe_sort",
                      "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows", "ie_gemm_rowdot", "ie_head_prepare",
                      "ie_heads_gemm", "ie_diff_combine", "ie_gated_residual_add", "ie_scale_rows", "ie_glu_act",
-                     "ie_mingru_scan"):
+                     "ie_mingru_scan", "ie_mingru_scan_hint"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -539,10 +540,12 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, kind: str, interleaved: bo
 
 def mingru_scan(z_pre: torch.Tensor, u_pre: torch.Tensor, g_pre: torch.Tensor, z_bias: torch.Tensor | None,
                 u_bias: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
-                slots: torch.Tensor, n_requests: int, write_state: bool = True) -> None:
+                slots: torch.Tensor, n_requests: int, write_state: bool = True, max_q_len: int = 0) -> None:
     """The minGRU over each request's tokens of the step, per channel: z = sigmoid(z_pre + z_bias), u = u_pre + u_bias,
     candidate = u + 1/2 where u >= 0 and sigmoid(u) where u < 0, S <- (1 - z) S + z candidate, out = S * silu(g_pre).
-    ``z_pre`` and ``u_pre`` are columns of one buffer (one row stride); ``state`` float32 [slots, width]."""
+    ``z_pre`` and ``u_pre`` are columns of one buffer (one row stride); ``state`` float32 [slots, width].  ``max_q_len``:
+    the most tokens a request brings, if known; for prompt portions the kernel that cuts a request's tokens into runs
+    (the recurrence is linear in the state) stands in for the token-by-token one."""
     n, width = out.shape
     assert z_pre.shape == u_pre.shape == g_pre.shape == (n, width) and z_pre.stride(0) == u_pre.stride(0)
     assert z_pre.stride(1) == 1 and u_pre.stride(1) == 1 and g_pre.stride(1) == 1 and out.stride(1) == 1
@@ -550,10 +553,10 @@ def mingru_scan(z_pre: torch.Tensor, u_pre: torch.Tensor, g_pre: torch.Tensor, z
     assert state.dtype is torch.float32 and state.is_contiguous() and state.shape[1:] == (width,)
     biases = [b for b in (z_bias, u_bias) if b is not None]
     assert all(b.dtype == biases[0].dtype and b.shape == (width,) and b.is_contiguous() for b in biases)
-    _check(core().ie_mingru_scan(_ptr(z_pre), _ptr(u_pre), z_pre.stride(0), _ptr(g_pre), g_pre.stride(0), _ptr(z_bias),
-                                 _ptr(u_bias), dtype_code(biases[0].dtype) if biases else IE_F32, _ptr(state), _ptr(out),
-                                 out.stride(0), _ptr(q_start), _ptr(slots), n_requests, width, 1 if write_state else 0,
-                                 dtype_code(out.dtype), _stream()), f"mingru_scan(width={width})")
+    _check(core().ie_mingru_scan_hint(_ptr(z_pre), _ptr(u_pre), z_pre.stride(0), _ptr(g_pre), g_pre.stride(0), _ptr(z_bias),
+                                      _ptr(u_bias), dtype_code(biases[0].dtype) if biases else IE_F32, _ptr(state), _ptr(out),
+                                      out.stride(0), _ptr(q_start), _ptr(slots), n_requests, width, 1 if write_state else 0,
+                                      dtype_code(out.dtype), int(max_q_len or 0), _stream()), f"mingru_scan(width={width})")
 
 
 # ------------------------------------------------------------------ a mixture of experts
@@ -755,6 +758,11 @@ def attention_wide_library(head_dim: int, v_head_dim: int):
         lib.ie_attention_wide.argtypes = [P] * 9 + [I] * 8 + [F, I, I, I, P]
         lib.ie_attention_wide.restype = c_int
         lib.ie_attention_wide_rows.restype = c_int
+        lib.ie_attention_wide_keys.restype = c_int
+        lib.ie_attention_wide_small.argtypes = [P] * 7 + [I] * 9 + [F] + [I] * 5 + [P, P]
+        lib.ie_attention_wide_small.restype = c_int
+        lib.ie_attention_wide_small_scratch.argtypes = [I, I, I, I]
+        lib.ie_attention_wide_small_scratch.restype = c_longlong
         _wide[key] = lib
         _apply_check_limits()
     return lib
@@ -779,6 +787,49 @@ def attention_wide(q, out, kpool, vpool, block_table, q_start, ctx_before, work_
                                  block_table.stride(0), n_work, n_heads, n_kv_heads, page_size, int(window or 0),
                                  float(scale), int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
            f"attention_wide(head_dim={head_dim}/{dv}, heads={n_heads}/{n_kv_heads})")
+
+
+def attention_wide_splits(head_dim: int, v_head_dim: int, keys: int, n_streams: int, n_sms: int | None = None) -> tuple[int, int]:
+    """(n_splits, split_keys) for ``attention_wide_small``: ``keys`` is the longest run of keys a request may see,
+    counted from the key tile's boundary below its first one; ``n_streams`` the (request tile, key head) pairs that each
+    walk such a run.  Enough splits to fill the device about twice, none shorter than two key tiles."""
+    tile = int(attention_wide_library(head_dim, v_head_dim).ie_attention_wide_keys())
+    n_tiles = max(1, -(-int(keys) // tile))
+    want = max(1, -(-2 * (n_sms or sm_count()) // max(1, n_streams)))
+    n_splits = max(1, min(want, n_tiles // 2 or 1))
+    per = -(-n_tiles // n_splits)
+    return -(-n_tiles // per), per * tile
+
+
+def attention_wide_small_scratch(head_dim: int, v_head_dim: int, n_requests: int, max_rows: int, n_kv_heads: int, n_splits: int) -> int:
+    """float32 words of scratch that ``attention_wide_small`` needs."""
+    return int(attention_wide_library(head_dim, v_head_dim).ie_attention_wide_small_scratch(n_requests, max_rows, n_kv_heads, n_splits))
+
+
+def attention_wide_small(q, out, kpool, vpool, block_table, q_start, ctx_before, n_requests: int, max_rows: int, n_heads,
+                         n_kv_heads, head_dim, page_size, window, scale, n_splits: int, split_keys: int,
+                         scratch: torch.Tensor | None, v_head_dim: int | None = None, chunk: int = 0,
+                         n_v_heads: int | None = None, v_row: int | None = None) -> None:
+    """``attention_wide`` for the requests of the step that bring at most ``max_rows`` (token, head-in-group) rows (decode
+    tokens, as a rule), without a work list: every (request, key head) is cut into ``n_splits`` runs of ``split_keys``
+    keys (``attention_wide_splits``), a block each, and a second kernel merges them through ``scratch`` (float32,
+    ``attention_wide_small_scratch`` words).  Rows of requests that bring more are left untouched."""
+    dv = int(v_head_dim or head_dim)
+    assert attention_wide_supports(q, out, head_dim, dv, v_row) and kpool.dtype is torch.bfloat16 and vpool.dtype is torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    lib = attention_wide_library(head_dim, dv)
+    if n_splits > 1:
+        need = int(lib.ie_attention_wide_small_scratch(n_requests, max_rows, n_kv_heads, n_splits))
+        assert scratch is not None and scratch.dtype is torch.float32 and scratch.is_contiguous() and scratch.numel() >= need
+    _check(lib.ie_attention_wide_small(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
+                                       _ptr(ctx_before), q.stride(0), out.stride(0), block_table.stride(0), n_requests,
+                                       int(max_rows), n_heads, n_kv_heads, page_size, int(window or 0), float(scale),
+                                       int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), int(n_splits), int(split_keys),
+                                       _ptr(scratch), _stream()),
+           f"attention_wide_small(head_dim={head_dim}/{dv}, heads={n_heads}/{n_kv_heads}, splits={n_splits})")
+    if n_splits > 1:
+        global LAUNCHES
+        LAUNCHES += 1       # the merge kernel
 
 
 def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim, biased: bool = False) -> int:

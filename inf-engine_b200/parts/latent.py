@@ -31,10 +31,17 @@ from .registry import build_position, position_class, register_mixer
 SMALL_REQUEST_TOKENS = 4      # requests that bring at most this many tokens get the split-key rows kernel
 
 
+WIDE_SMALL_MIN_GROUP = 4      # query heads a key head from which decode tokens take the tensor-core kernel too
+
+
 def attend_float32(q, out, kpool, vpool, ctx, kvctx, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
                    scale: float, chunk: int | None, n_v_heads: int | None = None, v_row: int | None = None) -> None:
-    """Causal attention of the step's queries over the paged keys in float32 arithmetic: the rows kernel for requests
-    of at most ``SMALL_REQUEST_TOKENS`` tokens, the tile kernel (with a work list of the others) for the rest."""
+    """Causal attention of the step's queries over the paged keys with float32 scores, maxima, weights and sums.
+    Requests of at most ``SMALL_REQUEST_TOKENS`` tokens (decode tokens): a block per (token, head) whose warps split the
+    keys, or, in bfloat16 storage with head sizes that are multiples of 16 and several query heads a key head, the
+    tensor-core kernel with the keys split over blocks (every key row is then loaded once for all those heads).  The
+    others (prompt portions), through a work list: the tensor-core kernel under the same conditions, else the float32
+    tile kernel."""
     group = n_heads // n_kv_heads
     max_rows = SMALL_REQUEST_TOKENS * group
     if ctx.max_q_len <= SMALL_REQUEST_TOKENS:
@@ -42,12 +49,25 @@ def attend_float32(q, out, kpool, vpool, ctx, kvctx, n_heads: int, n_kv_heads: i
     else:
         n_small = sum(1 for n in ctx.host["q_lens"] if n <= SMALL_REQUEST_TOKENS)
     extra = dict(v_head_dim=v_head_dim, chunk=chunk or 0, n_v_heads=n_v_heads, v_row=v_row)
+    wide = kpool.dtype is torch.bfloat16 and kernels.attention_wide_supports(q, out, head_dim, v_head_dim, v_row)
     if n_small:
-        kernels.attention_rows(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, ctx.n_requests,
-                               max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
+        if wide and group >= WIDE_SMALL_MIN_GROUP:
+            rows = kernels.ATTENTION_WIDE_ROWS
+            # the longest run of keys a small request may see, from the tile boundary below its first key
+            keys = min(ctx.keys_cap, chunk + SMALL_REQUEST_TOKENS) if chunk else ctx.keys_cap
+            n_splits, split_keys = kernels.attention_wide_splits(head_dim, v_head_dim, keys + 64,
+                                                                  ctx.n_requests * -(-max_rows // rows) * n_kv_heads)
+            words = kernels.attention_wide_small_scratch(head_dim, v_head_dim, ctx.n_requests, max_rows, n_kv_heads, n_splits)
+            scratch = ctx.rt.ws.take("attn_wide_scratch", (words,), torch.float32) if words else None
+            kernels.attention_wide_small(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, ctx.n_requests,
+                                         max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, n_splits,
+                                         split_keys, scratch, **extra)
+        else:
+            kernels.attention_rows(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, ctx.n_requests,
+                                   max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
         if n_small == ctx.n_requests:
             return
-    if kpool.dtype is torch.bfloat16 and kernels.attention_wide_supports(q, out, head_dim, v_head_dim, v_row):
+    if wide:
         # prompt portions in bfloat16 storage: tensor cores, with float32 scores and the weights in two bfloat16 terms
         work_req, work_pair0, n_work = ctx.attention_work(group, kernels.ATTENTION_WIDE_ROWS, max_rows if n_small else 0)
         kernels.attention_wide(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, work_req, work_pair0,

@@ -139,7 +139,7 @@ class MinGRU:
         proj = self.proj(x, rt.ws.take("mingru_proj", (n, 3 * w), rt.act_dtype))
         mixed = rt.ws.take("mingru_mixed", (n, w), rt.act_dtype)
         kernels.mingru_scan(proj[:, :w], proj[:, w:2 * w], proj[:, 2 * w:], self.z_bias, self.x_bias, cache.state, mixed,
-                            ctx.q_start, ctx.slots, ctx.n_requests, write_state=cache.write)
+                            ctx.q_start, ctx.slots, ctx.n_requests, write_state=cache.write, max_q_len=ctx.max_q_len)
         return self.o(mixed, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
 
 

@@ -250,13 +250,15 @@ def test_clamped_activation_in_the_epilogue_of_the_tensor_core_product(M, N, K, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_mingru_scan_kernel_carries_its_state_over_any_cut(dtype):
+@pytest.mark.parametrize("lens, in_runs", [([13, 1, 6], False), ([13, 1, 6], True), ([213, 1, 40], True)])
+def test_mingru_scan_kernel_carries_its_state_over_any_cut(dtype, lens, in_runs):
     """Three requests of unequal length in slots out of order, a padding row, gates from almost shut to almost open,
-    a state that is not zero at the start, a run that may not write."""
+    a state that is not zero at the start, a run that may not write; token by token, and with every request's tokens
+    cut into runs that are scanned side by side (more runs than tokens, and runs of unequal length)."""
     dt = TORCH[dtype]
     g = torch.Generator().manual_seed(8)
     width = 70
-    lens = [13, 1, 6]
+    hint = 1000 if in_runs else 0
     slots = [2, -1, 0, 3]
     zb, ub = torch.linspace(-6, 6, width).to(dt), torch.randn(width, generator=g).to(dt)
     state0 = torch.randn(5, width, generator=g)
@@ -293,10 +295,10 @@ def test_mingru_scan_kernel_carries_its_state_over_any_cut(dtype):
             out = torch.empty(x.shape[0], width, dtype=dt, device=DEV)
             before = state.clone()
             k().mingru_scan(x[:, :width], x[:, width:2 * width], x[:, 2 * width:], zb.to(DEV), ub.to(DEV), state, out,
-                            dev_i32(q_start), dev_i32(sl), len(sl), write_state=False)
+                            dev_i32(q_start), dev_i32(sl), len(sl), write_state=False, max_q_len=hint)
             assert torch.equal(state, before)
             k().mingru_scan(x[:, :width], x[:, width:2 * width], x[:, 2 * width:], zb.to(DEV), ub.to(DEV), state, out,
-                            dev_i32(q_start), dev_i32(sl), len(sl))
+                            dev_i32(q_start), dev_i32(sl), len(sl), max_q_len=hint)
             at = 0
             for j, s_ in enumerate(sl):
                 nrow = q_start[j + 1] - q_start[j]
@@ -456,7 +458,7 @@ def test_tensor_core_attention_with_float32_scores(dk, dv, n_heads, n_k, n_v, in
                 sc = (kk.double()[lo:p_ + 1, c] @ q.double()[t, h]) * scale
                 want[t, h] = torch.softmax(sc, 0) @ v.double()[lo:p_ + 1, c // (n_k // n_v)]
         wants.append(want)
-        qs.append(q.reshape(L, -1))
+        qs.append(q.reshape(L, n_heads * dk))
     n = sum(lens)
     qrows = torch.zeros(n, n_heads * dk + 8, dtype=dt)
     qrows[:, :n_heads * dk] = torch.cat(qs)
@@ -485,6 +487,91 @@ def test_tensor_core_attention_with_float32_scores(dk, dv, n_heads, n_k, n_v, in
                           window, scale, v_head_dim=dv, chunk=chunk or 0, n_v_heads=n_v, v_row=dk if in_keys else None)
     diff = (out2.double().cpu().reshape(n, n_heads, dv) - got).abs().amax(dim=(1, 2))
     assert bool((diff <= bound).all()), float(diff.max())
+
+
+@pytest.mark.parametrize("dk, dv, n_heads, n_k, n_v, in_keys, chunk, ps", [
+    (48, 32, 6, 1, 1, True, None, 8),            # six heads over one compressed row
+    (64, 128, 16, 4, 2, False, 37, 16),          # two maps a head over shared values, chunks
+    (256, 192, 40, 1, 1, True, None, 16),        # more rows than one tile holds: two tiles a request
+    (16, 16, 4, 4, 4, False, 50, 8),             # one head a key head
+])
+@pytest.mark.parametrize("n_splits", [1, 3, 0])
+def test_tensor_core_attention_of_decode_tokens_with_split_keys(dk, dv, n_heads, n_k, n_v, in_keys, chunk, ps, n_splits):
+    """Requests that bring one to three tokens at unequal lengths (one at the very start of its sequence, one right
+    after a chunk's edge), a request that brings too many rows and must be left alone, and a padding request without
+    tokens; one run of keys, three, or as many as the host would choose; against float64 and against the rows kernel."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(dk + dv + n_heads)
+    group = n_heads // n_k
+    scale = 0.5 / math.sqrt(dk)
+    lens, before = [1, 3, 2, 1, 9, 0, 1], [0, 200, 73, 74, 30, 0, 333]
+    max_rows = 4 * group
+    per = [-(-(b + L) // ps) for L, b in zip(lens, before)]
+    total_pages = sum(per) + 2
+    perm = torch.randperm(total_pages, generator=g)
+    kpool = torch.full((total_pages, n_k, ps, dk), float("nan"), dtype=dt)
+    vpool = kpool if in_keys else torch.full((total_pages, n_v, ps, dv), float("nan"), dtype=dt)
+    tables, qs, wants, at = [], [], [], 0
+    for L, b, npg in zip(lens, before, per):
+        T = b + L
+        kk = torch.randn(T, n_k, dk, generator=g).to(dt)
+        v = kk[:, :, :dv].clone() if in_keys else torch.randn(T, n_v, dv, generator=g).to(dt)
+        q = torch.randn(L, n_heads, dk, generator=g).to(dt)
+        pages = perm[at:at + npg]
+        at += npg
+        for t in range(T):
+            kpool[pages[t // ps], :, t % ps] = kk[t]
+            if not in_keys:
+                vpool[pages[t // ps], :, t % ps] = v[t]
+        table = torch.full((max(per),), -1, dtype=torch.int32)
+        table[:npg] = pages.to(torch.int32)
+        if chunk:
+            table[:((b // chunk) * chunk) // ps] = -1
+        tables.append(table)
+        want = torch.zeros(L, n_heads, dv, dtype=torch.float64)
+        for t in range(L):
+            p_ = b + t
+            lo = (p_ // chunk) * chunk if chunk else 0
+            for h in range(n_heads):
+                c = h // group
+                sc = (kk.double()[lo:p_ + 1, c] @ q.double()[t, h]) * scale
+                want[t, h] = torch.softmax(sc, 0) @ v.double()[lo:p_ + 1, c // (n_k // n_v)]
+        wants.append(want)
+        qs.append(q.reshape(L, n_heads * dk))
+    n = sum(lens)
+    starts = [0]
+    for L in lens:
+        starts.append(starts[-1] + L)
+    qd = torch.cat(qs).to(DEV)
+    kp = kpool.to(DEV)
+    vp = kp if in_keys else vpool.to(DEV)
+    extra = dict(v_head_dim=dv, chunk=chunk or 0, n_v_heads=n_v, v_row=dk if in_keys else None)
+    R = len(lens)
+    if n_splits == 0:
+        keys = min(max(b + L for L, b in zip(lens, before)), chunk + 4 if chunk else 1 << 30) + 64
+        n_splits, split_keys = k().attention_wide_splits(dk, dv, keys, R * -(-max_rows // 64) * n_k)
+        assert n_splits * split_keys >= keys
+    else:
+        tile = 64 if dk + dv <= 256 else 32
+        split_keys = -(-(max(b + L for L, b in zip(lens, before)) + 64) // (n_splits * tile)) * tile
+    words = k().attention_wide_small_scratch(dk, dv, R, max_rows, n_k, n_splits)
+    scratch = torch.full((max(words, 1),), float("nan"), device=DEV)
+    out = torch.full((n, n_heads * dv), 5.0, dtype=dt, device=DEV)
+    k().attention_wide_small(qd, out, kp, vp, torch.stack(tables).to(DEV), dev_i32(starts), dev_i32(before), R, max_rows, n_heads, n_k,
+                             dk, ps, None, scale, n_splits, split_keys, scratch if words else None, **extra)
+    out2 = torch.full((n, n_heads * dv), 5.0, dtype=dt, device=DEV)
+    k().attention_rows(qd, out2, kp, vp, torch.stack(tables).to(DEV), dev_i32(starts), dev_i32(before), R, max_rows, n_heads, n_k, dk,
+                       ps, None, scale, **extra)
+    got, got2 = out.double().cpu().reshape(n, n_heads, dv), out2.double().cpu().reshape(n, n_heads, dv)
+    big = slice(starts[4], starts[5])                        # nine tokens: more rows than max_rows, left alone by both
+    assert bool((got[big] == 5.0).all()) and bool((got2[big] == 5.0).all())
+    want = torch.cat(wants)
+    keep = torch.ones(n, dtype=torch.bool)
+    keep[big] = False
+    assert torch.isfinite(got[keep]).all()
+    bound = 1.2e-2 * want.abs().amax(dim=(1, 2)).clamp(min=0.05)
+    assert bool(((got - want).abs().amax(dim=(1, 2)) <= bound)[keep].all())
+    assert bool(((got - got2).abs().amax(dim=(1, 2)) <= bound)[keep].all())
 
 
 # =============================================================== whole models
