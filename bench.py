@@ -915,12 +915,13 @@ def run_family(args):
         zug, zb = rnd(N, 3 * W).to(bf), rnd(W).to(bf)
         sst, rout = torch.zeros(16, W, device=dev), torch.empty(N, W, device=dev, dtype=bf)
         u, ypre, gates, lam = rnd(N, W).to(bf), rnd(N, W).to(bf), rnd(N, 2 * W), rnd(W).to(bf)
-        scan = lambda n, qs, sl, R: kernels.mingru_scan(zug[:n, :W], zug[:n, W:2 * W], zug[:n, 2 * W:], zb, zb, sst, rout[:n], qs, sl, R)
+        scan = lambda n, qs, sl, R: kernels.mingru_scan(zug[:n, :W], zug[:n, W:2 * W], zug[:n, 2 * W:], zb, zb, sst, rout[:n], qs, sl, R,
+                                                        max_q_len=n // R)
         lru = lambda n, qs, sl, R: kernels.linear_recurrence(u[:n], ypre[:n], gates[:n, :W], gates[:n, W:], zb, zb, lam, sst, rout[:n],
                                                              qs, sl, R, 8.0)
         add("minGRU scan, prompt of 2,048 tokens (one request)", "linear recurrent unit scan, prompt",
             timed(lambda: scan(N, qs1, sl1, 1), reps=5), timed(lambda: lru(N, qs1, sl1, 1), reps=5),
-            N * W * (3 * 2 + 2), N * W * (2 + 2 + 4 + 4 + 2), note="a scan over tokens, a channel a thread")
+            N * W * (3 * 2 + 2), N * W * (2 + 2 + 4 + 4 + 2), note="the request's tokens cut into runs that are scanned side by side")
         add("minGRU scan, decode b8", "linear recurrent unit scan, decode",
             timed(lambda: scan(B, qs8, sl8, B)), timed(lambda: lru(B, qs8, sl8, B)),
             B * W * (3 * 2 + 2 + 8), B * W * (2 + 2 + 4 + 4 + 2 + 8))

@@ -323,7 +323,12 @@ __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
   }
 }
 
-// the splits of a tile become its output rows: out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m = max_s m_s
+// the splits of a tile become its output rows: out = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m = max_s m_s.
+// A warp a row (block z takes rows 4 z .. 4 z + 3 of the tile): its lanes find m over the splits together, then walk the
+// splits with the row's values spread over the lanes, so every load of a partial output is one contiguous piece.
+constexpr int MERGE_ROWS = THREADS / 32;
+constexpr int MERGE_SLOTS = (DV + 63) / 64;           // pairs of values a lane holds
+
 __global__ void __launch_bounds__(THREADS) attention_wide_merge_kernel(WideParams p) {
   pdl_trigger();
   pdl_wait();
@@ -334,29 +339,44 @@ __global__ void __launch_bounds__(THREADS) attention_wide_merge_kernel(WideParam
   const int n_pairs = (p.q_start[r_id + 1] - q0) * group;
   if (n_pairs > p.max_rows || pair0 >= n_pairs) return;
   const int rows = min(BM, n_pairs - pair0);
+  const int lane = threadIdx.x & 31;
+  const int r = (int)blockIdx.z * MERGE_ROWS + ((int)threadIdx.x >> 5);
+  if (r >= rows) return;                              // (the whole warp)
   const size_t part0 = ((size_t)blockIdx.x * p.n_kv_heads + c) * p.n_splits;
-  for (int idx = threadIdx.x; idx < rows * (DV / 2); idx += THREADS) {
-    const int r = idx / (DV / 2), d = (idx - r * (DV / 2)) * 2;
-    float m_all = -INFINITY;
-    for (int s = 0; s < p.n_splits; ++s) m_all = fmaxf(m_all, p.part_ml[((part0 + s) * BM + r) * 2]);
-    float l_all = 0.f, ox = 0.f, oy = 0.f;
-    if (m_all != -INFINITY) {
-      for (int s = 0; s < p.n_splits; ++s) {
-        const size_t row = (part0 + s) * BM + r;
-        const float m_s = p.part_ml[row * 2];
-        if (m_s == -INFINITY) continue;
-        const float w = exp2f(m_s - m_all);
-        l_all = fmaf(p.part_ml[row * 2 + 1], w, l_all);
-        const float2 v = *reinterpret_cast<const float2*>(p.part_o + row * DV + d);
-        ox = fmaf(v.x, w, ox);
-        oy = fmaf(v.y, w, oy);
+  float m_all = -INFINITY;
+  for (int s = lane; s < p.n_splits; s += 32) m_all = fmaxf(m_all, p.part_ml[((part0 + s) * BM + r) * 2]);
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, k));
+  float l_all = 0.f;
+  float2 acc[MERGE_SLOTS];
+#pragma unroll
+  for (int i = 0; i < MERGE_SLOTS; ++i) acc[i] = make_float2(0.f, 0.f);
+  if (m_all != -INFINITY) {
+#pragma unroll 4
+    for (int s = 0; s < p.n_splits; ++s) {
+      const size_t row = (part0 + s) * BM + r;
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + row * 2);
+      const float w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m_all);
+      l_all = fmaf(ml.y, w, l_all);
+#pragma unroll
+      for (int i = 0; i < MERGE_SLOTS; ++i) {
+        const int d = (i * 32 + lane) * 2;
+        if (d < DV && w != 0.f) {
+          const float2 v = *reinterpret_cast<const float2*>(p.part_o + row * DV + d);
+          acc[i].x = fmaf(v.x, w, acc[i].x);
+          acc[i].y = fmaf(v.y, w, acc[i].y);
+        }
       }
     }
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-    const int pr = pair0 + r;
-    const int t = pr / group, j = pr - t * group;
-    bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + (size_t)(c * group + j) * DV + d;
-    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(ox * inv, oy * inv);
+  }
+  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+  const int pr = pair0 + r;
+  const int t = pr / group, j = pr - t * group;
+  bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + (size_t)(c * group + j) * DV;
+#pragma unroll
+  for (int i = 0; i < MERGE_SLOTS; ++i) {
+    const int d = (i * 32 + lane) * 2;
+    if (d < DV) *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(acc[i].x * inv, acc[i].y * inv);
   }
 }
 
@@ -443,7 +463,7 @@ extern "C" int ie_attention_wide_small(const void* q, void* out, const void* kpo
   const dim3 grid(n_requests * p.tiles, n_kv_heads, n_splits);
   int st = launch_k(attention_wide_kernel, grid, THREADS, smem, stream, p);
   if (st != IE_OK || n_splits == 1) return st;
-  return launch_k(attention_wide_merge_kernel, dim3(grid.x, grid.y), THREADS, 0, stream, p);
+  return launch_k(attention_wide_merge_kernel, dim3(grid.x, grid.y, BM / MERGE_ROWS), THREADS, 0, stream, p);
 }
 
 IE_CHECK_API(attention_wide)

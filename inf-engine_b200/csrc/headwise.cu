@@ -145,19 +145,22 @@ extern "C" int ie_head_prepare(void* q, int q_stride, int q_heads, int q_hd, int
 #define HG_ROWS 8
 #define HG_THREADS 128
 
-// A block takes `groups` x HG_ROWS rows of one head: its threads are `groups` row groups of HG_THREADS / groups columns,
-// so that a narrow output (fewer columns than threads) still keeps every thread busy.
+// A block takes `groups` x HG_ROWS rows of one head: its threads are `groups` row groups of blockDim.x / groups columns,
+// so that a narrow output (fewer columns than threads) still keeps every thread busy.  Block z takes the columns
+// z * z_cols .. (z + 1) * z_cols - 1: a few rows (decode tokens) are spread over many small blocks, a column each thread.
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(HG_THREADS) heads_gemm_kernel(const TX* __restrict__ x, int x_stride, int x_head,
                                                                 const TW* __restrict__ w, TO* __restrict__ out,
-                                                                int o_stride, int o_head, int M, int K, int N, int groups) {
+                                                                int o_stride, int o_head, int M, int K, int N, int groups,
+                                                                int z_cols) {
   extern __shared__ float xs[];          // [groups * HG_ROWS][K]
   pdl_trigger();
   pdl_wait();
-  const int block_rows = groups * HG_ROWS, cols = HG_THREADS / groups;
+  const int threads = blockDim.x;
+  const int block_rows = groups * HG_ROWS, cols = threads / groups;
   const int m0 = blockIdx.x * block_rows, h = blockIdx.y;
   const int rows = min(block_rows, M - m0);
-  for (int i = threadIdx.x; i < block_rows * K; i += HG_THREADS) {
+  for (int i = threadIdx.x; i < block_rows * K; i += threads) {
     const int r = i / K, k = i - r * K;
     xs[i] = r < rows ? to_f32(x[(size_t)(m0 + r) * x_stride + h * x_head + k]) : 0.f;
   }
@@ -165,10 +168,12 @@ __global__ void __launch_bounds__(HG_THREADS) heads_gemm_kernel(const TX* __rest
   const TW* wh = w + (size_t)h * K * N;
   const int rg = threadIdx.x / cols, r0 = rg * HG_ROWS;
   const float* xg = xs + (size_t)r0 * K;
-  for (int j = threadIdx.x - rg * cols; j < N; j += cols) {
+  const int j_end = min(N, ((int)blockIdx.z + 1) * z_cols);
+  for (int j = (int)blockIdx.z * z_cols + threadIdx.x - rg * cols; j < j_end; j += cols) {
     float acc[HG_ROWS];
 #pragma unroll
     for (int r = 0; r < HG_ROWS; ++r) acc[r] = 0.f;
+#pragma unroll 16
     for (int k = 0; k < K; ++k) {
       const float wv = to_f32(wh[(size_t)k * N + j]);
 #pragma unroll
@@ -190,6 +195,13 @@ extern "C" int ie_heads_gemm(const void* x, int x_dtype, int x_stride, int x_hea
   const size_t smem = sizeof(float) * groups * HG_ROWS * (size_t)K;
   if (smem > 96 * 1024) return IE_BAD_SIZE;
   dim3 grid((M + groups * HG_ROWS - 1) / (groups * HG_ROWS), H);
+  // few rows (decode tokens): a warp a block and 32 columns each, so that the heads' weights stream through many blocks
+  int threads = HG_THREADS, z_cols = N;
+  if (groups == 1 && grid.x * (size_t)H < 256 && N > 32) {
+    threads = 32;
+    z_cols = 32;
+    grid.z = (N + 31) / 32;
+  }
 #define HG_GO(TX, TW, TO)                                                                                           \
   {                                                                                                                 \
     if (smem > 48 * 1024) {                                                                                         \
@@ -197,8 +209,8 @@ extern "C" int ie_heads_gemm(const void* x, int x_dtype, int x_stride, int x_hea
                                            (int)smem);                                                             \
       if (e != cudaSuccess) return (int)e;                                                                          \
     }                                                                                                               \
-    return launch_k(heads_gemm_kernel<TX, TW, TO>, grid, HG_THREADS, smem, stream, (const TX*)x, x_stride, x_head,  \
-                    (const TW*)w, (TO*)out, o_stride, o_head, M, K, N, groups);                                     \
+    return launch_k(heads_gemm_kernel<TX, TW, TO>, grid, threads, smem, stream, (const TX*)x, x_stride, x_head,     \
+                    (const TW*)w, (TO*)out, o_stride, o_head, M, K, N, groups, z_cols);                             \
   }
   if (x_dtype == IE_F32 && w_dtype == IE_F32 && o_dtype == IE_F32) HG_GO(float, float, float);
   if (x_dtype == IE_F32 && w_dtype == IE_BF16 && o_dtype == IE_F32) HG_GO(float, bf16, float);
