@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(HG_THREADS) heads_gemm_kernel(const TX* __rest
     float acc[HG_ROWS];
 #pragma unroll
     for (int r = 0; r < HG_ROWS; ++r) acc[r] = 0.f;
-#pragma unroll 16
+#pragma unroll 8
     for (int k = 0; k < K; ++k) {
       const float wv = to_f32(wh[(size_t)k * N + j]);
 #pragma unroll

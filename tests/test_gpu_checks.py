@@ -29,7 +29,7 @@ long_prompt = [(7 * i + 3) % 1000 for i in range(150)]
 out = engine.run_offline([Request(0, long_prompt, 4), Request(1, [11, 400, 23], 4)])   # raises if a check had failed
 result = {{"clean": kernels.read_check_words(), "generated": [len(out[0]), len(out[1])]}}
 
-# Now the checker is told that the pool has 3 pages and 48 slots and the vocabulary 10 tokens: pages, slots and
+# Now the checks are told that the pool has 3 pages and 48 slots and the vocabulary 10 tokens: pages, slots and
 # tokens that are perfectly valid trip it, and the kernels leave them alone (no page, no slot), so nothing is
 # read or written out of bounds whatever the check does.
 kernels.set_check_limits(3, 48, 10)
