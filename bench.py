@@ -986,17 +986,25 @@ def run_family(args):
         absorb, qc = (rnd(H, qd, rd) * 0.1).to(bf), torch.empty(N, H * rd, device=dev, dtype=bf)
         ag, gts = rnd(W // 256, 256, 256).to(bf), torch.empty(N, W, device=dev)
         like_hg = timed(lambda: kernels.gemm_simt_batched(u, ag, gts))
-        rec = {"kernel": "queries into the compressed space, a product a head (float32 on CUDA cores), prompt",
-               "like": "block-diagonal gate product, prompt (float32 on CUDA cores)"}
-        rec["ms"], rec["like_ms"] = timed(lambda: kernels.heads_gemm(ql, qd, absorb, qc, rd)), like_hg
-        rec["tflops_f32"], rec["like_tflops_f32"] = 2 * N * H * qd * rd / (rec["ms"] * 1e-3) / 1e12, 2 * N * W * 256 / (like_hg * 1e-3) / 1e12
-        rows.append(rec)
+        from inf_engine_b200.parts.latent import heads_product
+        like_tf = 2 * N * W * 256 / (like_hg * 1e-3) / 1e12
         expand, mixed, heads = (rnd(H, kr, hd) * 0.1).to(bf), torch.empty(N, H * kr, device=dev, dtype=bf), torch.empty(N, H * hd, device=dev, dtype=bf)
-        rec = {"kernel": "values out of the compressed space, a product a head, prompt", "like": rec["like"], "like_ms": like_hg,
-               "like_tflops_f32": rec["like_tflops_f32"]}
-        rec["ms"] = timed(lambda: kernels.heads_gemm(mixed, kr, expand, heads, hd))
-        rec["tflops_f32"] = 2 * N * H * kr * hd / (rec["ms"] * 1e-3) / 1e12
-        rows.append(rec)
+        for what, run, flops_row in (
+                ("queries into the compressed space, a product a head", lambda n, f: f(ql[:n], qd, absorb, qc[:n], rd), 2 * H * qd * rd),
+                ("values out of the compressed space, a product a head", lambda n, f: f(mixed[:n], kr, expand, heads[:n], hd), 2 * H * kr * hd)):
+            # a prompt portion: the library's batched product on tensor cores; decode tokens: this package's kernel
+            rec = {"kernel": what + ", prompt (library batched product)", "like": "block-diagonal gate product, prompt (float32 on CUDA cores)",
+                   "ms": timed(lambda: run(N, heads_product)), "like_ms": like_hg, "like_tflops_f32": like_tf}
+            rec["tflops"] = N * flops_row / (rec["ms"] * 1e-3) / 1e12
+            rec["frac_of_bf16"] = rec["tflops"] / pk["bf16_tflops"]
+            rows.append(rec)
+            rec = {"kernel": what + ", prompt, this package's kernel (float32 on CUDA cores; what the 32-bit path runs)", "like": rec["like"],
+                   "ms": timed(lambda: run(N, kernels.heads_gemm)), "like_ms": like_hg, "like_tflops_f32": like_tf}
+            rec["tflops_f32"] = N * flops_row / (rec["ms"] * 1e-3) / 1e12
+            rows.append(rec)
+            ms = timed(lambda: run(B, heads_product))
+            rows.append({"kernel": what + ", decode b8", "like": "none", "ms": ms, "like_ms": 0.0,
+                         "frac_of_hbm": H * (flops_row // (2 * H)) * 2 / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]})
         lat_att = lambda ctx, n: attend_float32(qc[:n], mixed[:n], lpool, lpool, ctx, ctx.kv[0], H, 1, rd, kr, qd ** -0.5, None,
                                                 n_v_heads=1, v_row=rd)
         add("attention, prompt (latent: %d heads over one row of %d, every key)" % (H, rd), "attention, prompt (window of 1,024 + 4 kept keys)",

@@ -3,7 +3,7 @@
 ``LatentAttention``: per token the cache holds one row ``[c, k_rot]``: the compressed vector c (``kv_rank`` numbers,
 RMS-normed) and a rotated key part that all heads share.  A head's unrotated key is ``k_up_h c`` and its value
 ``v_up_h c``, so its score is ``q_un . (k_up_h c) + q_rot . k_rot = (k_up_h^T q_un) . c + q_rot . k_rot``: the query is
-carried over to the compressed space once (a product per head, ``kernels.heads_gemm``), every head then reads the SAME
+carried over to the compressed space once (a product per head, ``heads_product``), every head then reads the SAME
 cached rows (attention with one key head whose values are the first ``kv_rank`` dimensions of its keys), and the
 head's output ``v_up_h (sum_j w_j c_j)`` is one more product per head.  Nothing per head is ever stored per token.
 
@@ -76,6 +76,25 @@ def attend_float32(q, out, kpool, vpool, ctx, kvctx, n_heads: int, n_kv_heads: i
     work_req, work_pair0, n_work = ctx.attention_work(group, 32, max_rows if n_small else 0)
     kernels.attention_general(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, work_req, work_pair0,
                               n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
+
+
+LIBRARY_HEADS_MIN_ROWS = 64   # rows from which a per-head product in bfloat16 goes to the library's batched product
+
+
+def heads_product(x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor, o_head: int) -> None:
+    """A product per head, ``out[m, h * o_head + j] = sum_k x[m, h * x_head + k] * w[h, k, j]`` with float32 sums, as
+    ``Linear`` chooses for a projection: float32 operands and few rows (decode tokens, inside captured steps) take this
+    package's kernel, whose sums do not depend on the batch; prompt portions in bfloat16 take the library's batched
+    product on tensor cores, with the heads as the batch (the rows of ``x`` and ``out`` are read and written in place
+    through their strides)."""
+    H, K, N = w.shape
+    m = x.shape[0]
+    if (m >= LIBRARY_HEADS_MIN_ROWS and x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16
+            and out.dtype is torch.bfloat16 and x.stride(1) == 1 and out.stride(1) == 1):
+        torch.bmm(x.as_strided((H, m, K), (x_head, x.stride(0), 1)), w,
+                  out=out.as_strided((H, m, N), (o_head, out.stride(0), 1)))
+        return
+    kernels.heads_gemm(x, x_head, w, out, o_head)
 
 
 def _rotation(position):
@@ -153,12 +172,12 @@ class LatentAttention:
                              eps=s.norm_eps, inv_freq=inv_freq, rot_dims=rot_dims, q_rot_off=s.head_dim, k_rot_off=kr,
                              neighbours=neighbours, mult=mult)
         qc = rt.ws.take("latent_qc", (n, H * self.row_dim), rt.act_dtype)
-        kernels.heads_gemm(q, self.q_dim, self.absorb, qc, self.row_dim)
+        heads_product(q, self.q_dim, self.absorb, qc, self.row_dim)
         mixed = rt.ws.take("latent_mixed", (n, H * kr), rt.act_dtype)
         attend_float32(qc, mixed, cache.k, cache.k, ctx, kvctx, H, 1, self.row_dim, kr, float(s.scale), s.chunk,
                        n_v_heads=1, v_row=self.row_dim)
         heads = rt.ws.take("latent_heads", (n, H * s.v_head_dim), rt.act_dtype)
-        kernels.heads_gemm(mixed, kr, self.expand, heads, s.v_head_dim)
+        heads_product(mixed, kr, self.expand, heads, s.v_head_dim)
         return self.o(heads, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
 
 

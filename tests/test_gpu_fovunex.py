@@ -175,6 +175,28 @@ def test_heads_gemm_kernel(dtype, m, heads, kd, nd):
         assert bool((out[:, h * (nd + 1) + nd] == 9.0).all())
 
 
+@pytest.mark.parametrize("m, heads, kd, nd", [(64, 3, 12, 24), (150, 5, 14, 6), (300, 2, 48, 80), (5, 2, 16, 16)])
+def test_per_head_product_of_prompt_portions_in_bfloat16(m, heads, kd, nd):
+    """From 64 rows on the bfloat16 product goes to the library's batched product, read and written in place through
+    strided rows (heads that are not packed, columns that must stay untouched); below that the kernel runs."""
+    from inf_engine_b200.parts.latent import heads_product
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(m, heads * (kd + 3) + 2, generator=g).bfloat16()
+    w = torch.randn(heads, kd, nd, generator=g).bfloat16()
+    out = torch.full((m, heads * (nd + 1) + 4), 9.0, dtype=torch.bfloat16, device=DEV)
+    out2 = out.clone()
+    heads_product(x.to(DEV), kd + 3, w.to(DEV), out, nd + 1)
+    k().heads_gemm(x.to(DEV), kd + 3, w.to(DEV), out2, nd + 1)
+    for h in range(heads):
+        want = x.double()[:, h * (kd + 3):h * (kd + 3) + kd] @ w[h].double()
+        assert close(out[:, h * (nd + 1):h * (nd + 1) + nd], want, "bfloat16")
+        assert bool((out[:, h * (nd + 1) + nd] == 9.0).all())
+        # the two ways differ by the order of a float32 sum only: at most one bfloat16 step of the result
+        d = (out[:, h * (nd + 1):h * (nd + 1) + nd].double() - out2[:, h * (nd + 1):h * (nd + 1) + nd].double()).abs().cpu()
+        assert bool((d <= 2.0 ** -7 * want.abs().clamp(min=0.25)).all())
+    assert bool((out[:, heads * (nd + 1):] == 9.0).all())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, kv, dv, gated", [(4, 2, 24, True), (3, 3, 12, False), (5, 1, 6, True), (2, 1, 80, True),
                                                   (6, 2, 32, True), (5, 5, 64, True), (3, 1, 128, False), (2, 2, 256, True)])
