@@ -196,7 +196,7 @@ __global__ void mingru_scan_kernel(const T* __restrict__ z_pre, const T* __restr
 // state through the MGS_SEG pairs, pass two repeats every run from its true starting state and writes the outputs.
 // Twice the arithmetic and reads (the second time from cache) for a dependent chain of T / MGS_SEG + MGS_SEG steps.
 #define MGS_CH 32
-#define MGS_SEG 16
+#define MGS_SEG 32
 
 template <typename T, typename TB>
 __global__ void __launch_bounds__(MGS_CH * MGS_SEG) mingru_scan_segments_kernel(
