@@ -27,11 +27,53 @@ __global__ void gated_residual_add_kernel(float* __restrict__ residual, const T*
   residual[i] = fmaf(sigmoid_f(g), to_f32(y[(size_t)r * y_stride + c]), residual[i]);
 }
 
+// bfloat16 rows whose width and strides are multiples of 8: eight coordinates a thread, 16-byte loads and stores
+template <typename TB>
+__global__ void gated_residual_add_bf16_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ y, int y_stride,
+                                                   const bf16* __restrict__ gate, int gate_stride,
+                                                   const TB* __restrict__ bias, size_t n_vec, int d8) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const size_t r = i / d8;
+  const int c = (int)(i - r * d8) * 8;
+  const uint4 yv = *reinterpret_cast<const uint4*>(y + r * y_stride + c);
+  const uint4 gv = *reinterpret_cast<const uint4*>(gate + r * gate_stride + c);
+  const __nv_bfloat162* y2 = reinterpret_cast<const __nv_bfloat162*>(&yv);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  float4* res = reinterpret_cast<float4*>(residual + r * (size_t)d8 * 8 + c);
+  float4 a = res[0], b = res[1];
+  float* out[2] = {&a.x, &b.x};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 yf = __bfloat1622float2(y2[k]), gf = __bfloat1622float2(g2[k]);
+    const float b0 = bias != nullptr ? to_f32(bias[c + 2 * k]) : 0.f, b1 = bias != nullptr ? to_f32(bias[c + 2 * k + 1]) : 0.f;
+    float* o = out[k >> 1] + 2 * (k & 1);
+    o[0] = fmaf(sigmoid_f(gf.x + b0), yf.x, o[0]);
+    o[1] = fmaf(sigmoid_f(gf.y + b1), yf.y, o[1]);
+  }
+  res[0] = a;
+  res[1] = b;
+}
+
 extern "C" int ie_gated_residual_add(float* residual, const void* y, int y_stride, const void* gate, int gate_stride,
                                      const void* bias, int bias_dtype, int n_rows, int d, int act_dtype,
                                      cudaStream_t stream) {
   const size_t n = (size_t)n_rows * d;
   if (n == 0) return IE_OK;
+  if (act_dtype == IE_BF16 && d % 8 == 0 && y_stride % 8 == 0 && gate_stride % 8 == 0 &&
+      (((uintptr_t)residual | (uintptr_t)y | (uintptr_t)gate) & 15) == 0) {
+    const size_t n_vec = n / 8;
+    const unsigned vblocks = (unsigned)((n_vec + 255) / 256);
+    if (bias_dtype == IE_F32)
+      return launch_k(gated_residual_add_bf16_vec_kernel<float>, vblocks, 256, 0, stream, residual, (const bf16*)y, y_stride,
+                      (const bf16*)gate, gate_stride, (const float*)bias, n_vec, d / 8);
+    if (bias_dtype == IE_BF16)
+      return launch_k(gated_residual_add_bf16_vec_kernel<bf16>, vblocks, 256, 0, stream, residual, (const bf16*)y, y_stride,
+                      (const bf16*)gate, gate_stride, (const bf16*)bias, n_vec, d / 8);
+    return IE_BAD_DTYPE;
+  }
   const unsigned blocks = (unsigned)((n + 255) / 256);
 #define GR_GO(T, TB)                                                                                             \
   return launch_k(gated_residual_add_kernel<T, TB>, blocks, 256, 0, stream, residual, (const T*)y, y_stride,     \

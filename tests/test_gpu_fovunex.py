@@ -217,12 +217,12 @@ def test_diff_combine_kernel(dtype, heads, kv, dv, gated):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_gates_scale_and_activation_kernels(dtype):
+@pytest.mark.parametrize("n, d, pad", [(11, 37, 3), (70, 64, 8)])       # odd sizes; rows that take the 16-byte forms
+def test_gates_scale_and_activation_kernels(dtype, n, d, pad):
     dt = TORCH[dtype]
     g = torch.Generator().manual_seed(7)
-    n, d = 11, 37
     res = torch.randn(n, d, generator=g)
-    y, gp = torch.randn(n, d + 3, generator=g).to(dt), (3 * torch.randn(n, d, generator=g)).to(dt)
+    y, gp = torch.randn(n, d + pad, generator=g).to(dt), (3 * torch.randn(n, d, generator=g)).to(dt)
     b = torch.randn(d, generator=g).to(dt)
     r = res.to(DEV)
     k().gated_residual_add(r, y.to(DEV)[:, :d], gp.to(DEV), b.to(DEV))
