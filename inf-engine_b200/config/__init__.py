@@ -1,5 +1,6 @@
 from .barerax import BareraxConfig
 from .fovunex import FovunexConfig
+from .gavatar import GavatarConfig
 from .kipezen import KipezenConfig
 from .llama import ConfigError, LlamaConfig
 from .registry import (

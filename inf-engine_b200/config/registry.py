@@ -122,3 +122,11 @@ def _fovunex(d: dict):
 
 
 register_architecture("Fovunex", _fovunex)
+
+
+def _gavatar(d: dict, tensor_shapes: dict | None = None):
+    from .gavatar import GavatarConfig
+    return GavatarConfig.from_dict(d, tensor_shapes)
+
+
+register_architecture("Gavatar", _gavatar, reads_shapes=True)

@@ -160,6 +160,77 @@ class LatentAttentionSpec(MixerSpec):
     k_up: str = ""
     v_up: str = ""
     o_proj: str = ""
+    # Queries through a compressed vector of their own: c_q = RMSnorm(q_down x) with the gain q_norm (eps norm_eps),
+    # then q = q_proj c_q (q_proj is then [heads * (head_dim + rot_dim), q_rank]).  q_rank 0: q = q_proj x.
+    q_rank: int = 0
+    q_down: str = ""
+    q_norm: str = ""
+    window: int | None = None      # a query sees itself and the window - 1 keys before it (None: every earlier key)
+    sink: str | None = None        # tensor [n_heads]: exp(sink_h) joins the softmax's denominator of head h; it has no
+                                   # key and no value and is not scaled
+    head_gate: str | None = None   # tensor [n_heads, hidden]: head h's output is multiplied by sigmoid(head_gate x)_h
+
+
+@dataclass(frozen=True)
+class TalkingAttentionSpec(MixerSpec):
+    """Grouped-query softmax attention without positions whose weights are mixed across heads after the softmax.
+
+    q, k, v = q_proj x, k_proj x, v_proj x (+ biases); with ``qk_norm`` every query and key head, with ``v_norm`` every
+    value head (as it is cached), is divided by its root mean square (``norm_eps`` inside the root, no gain).
+    score = q . k * scale under a causal mask (``window``: a query sees itself and the window - 1 keys before it);
+    ordinary softmax per head; then weight_h(i, j) <- sum_g talk[h, g] weight_g(i, j) (``talk`` [heads, heads], None:
+    no mixing) and head h applies its mixed weights to the values of its own key/value head h // (heads / kv heads).
+    The concatenated heads are multiplied by sigmoid(gate_proj x) element by element (None: no gate), then ``o_proj``."""
+
+    hidden: int = 0
+    n_heads: int = 0
+    n_kv_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    scale: float = 1.0
+    norm_eps: float = 1e-6
+    qk_norm: bool = True
+    v_norm: bool = True
+    window: int | None = None
+    q_proj: str = ""
+    k_proj: str = ""
+    v_proj: str = ""
+    q_bias: str | None = None
+    k_bias: str | None = None
+    v_bias: str | None = None
+    talk: str | None = None
+    gate_proj: str | None = None
+    o_proj: str = ""
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(MixerSpec):
+    """The matrix memory of xLSTM (mLSTM) with exponential gates and a running maximum.
+
+    q = q_proj x * head_dim^-1/2 and k = k_proj x (heads x head_dim), v = v_proj x (heads x v_head_dim).  Per head the
+    log input gate i = cap * tanh((i_proj x + i_bias) / cap) and the log forget gate f = logsigmoid(cap * tanh((f_proj x
+    + f_bias) / cap)), cap = ``gate_cap``.  With S, n and the maximum m all zero at the start:
+        m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k alone;  m <- m'
+        o = S^T q / (max(|n . q|, exp(-m)) + denom_eps)
+    Each head's o is divided by its root mean square (norm_eps); the heads, side by side, are multiplied by ``out_gain``
+    (all heads' size) and by sigmoid(gate_proj x), then ``o_proj``."""
+
+    hidden: int = 0
+    n_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    gate_cap: float = 15.0
+    norm_eps: float = 1e-6
+    q_proj: str = ""
+    k_proj: str = ""
+    v_proj: str = ""
+    i_proj: str = ""
+    i_bias: str = ""
+    f_proj: str = ""
+    f_bias: str = ""
+    gate_proj: str = ""
+    out_gain: str = ""
+    o_proj: str = ""
 
 
 @dataclass(frozen=True)
@@ -386,6 +457,10 @@ class RoutedExpertsSpec(FeedForwardSpec):
     expert_prefix: str = ""        # expert e's tensors are <prefix><e>.gate / .up / .down
     shared: GatedMLPSpec | None = None
     shared_gate: str | None = None
+    # ``score`` "softmax_top": the logits are router x + ``router_bias`` (float32); the ``top`` largest are chosen (no
+    # groups, no correction) and their weights are the softmax over the chosen logits alone, times ``route_scale``.
+    score: str = "sigmoid"
+    router_bias: str | None = None
 
 
 @dataclass(frozen=True)
@@ -404,6 +479,13 @@ class BlockSpec:
     mixer_gate_bias: str | None = None
     ff_gate: str | None = None
     ff_gate_bias: str | None = None
+    # "sandwich": x += out_norm(part(norm(x))): a norm before and after each sublayer (``mixer_norm`` / ``ff_norm``
+    # before, these two after).  ``token_shift`` names a tensor [hidden]: what the mixer reads, h = mixer_norm(x), is
+    # replaced by h + (h' - h) * token_shift with h' the h of the token before (zeros before the first); the last h of a
+    # sequence is state of the run beside the mixer's own.
+    mixer_out_norm: NormSpec | None = None
+    ff_out_norm: NormSpec | None = None
+    token_shift: str | None = None
 
 
 @dataclass(frozen=True)
@@ -458,3 +540,18 @@ class ReinjectDecoderSpec(ModelSpec):
     embedding_scale: float = 1.0
     reinject_before: tuple[int, ...] = ()
     kind: str = "reinject_decoder"
+
+
+@dataclass(frozen=True)
+class PassOffsetDecoderSpec(ModelSpec):
+    """A decoder whose first residual is the token embedding times ``embedding_scale`` plus, with ``sinusoid_base`` > 0,
+    a sinusoidal position vector (entry 2i: sin(p base^(-2i / hidden)), entry 2i + 1: the cosine of the same angle), and
+    which adds a learned vector to the stream right before some schedule entries: ``offset_before`` lists (entry, row)
+    pairs, and row r of the tensor ``pass_offsets`` ([rows, hidden]) is added before that entry runs (a group of layers
+    run several times in a row takes the vector of its pass at the start of each pass, the first too)."""
+
+    embedding_scale: float = 1.0
+    sinusoid_base: float = 0.0
+    pass_offsets: str | None = None
+    offset_before: tuple[tuple[int, int], ...] = ()
+    kind: str = "pass_offset_decoder"

@@ -59,7 +59,18 @@ struct AttnGeneralParams {
   int n_v_heads;            // value heads in the value pool; kv head c reads value head c / (n_kv_heads / n_v_heads)
   int v_row;                // elements between two value rows of the value pool (the value size, or a key row's size
                             // when the values are the first dimensions of the keys and both pools are one)
+  const float* sink;        // [n_heads] or null: the softmax's denominator also holds exp(sink[head]), a term that has
+                            // no key and no value and is not scaled
 };
+
+// the normaliser of a row whose visible keys gave the sum l at the maximum m, with the sink's term added
+__device__ __forceinline__ float inv_with_sink(float l, float m, const float* sink, int head, float out_scale) {
+  if (sink == nullptr || m == -INFINITY) return l > 0.f ? out_scale / l : 0.f;
+  const float sk = sink[head];
+  const float m2 = fmaxf(m, sk);
+  const float f = expf(m - m2);
+  return out_scale * f / (l * f + expf(sk - m2));
+}
 
 template <typename T>
 __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGeneralParams p) {
@@ -220,7 +231,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   if (row_valid) {
     const int j = my_pair - my_t * group;
     T* o = (T*)p.out + (size_t)(q0 + my_t) * p.out_stride + (c * group + j) * hdv;
-    const float inv = l_run > 0.f ? p.out_scale / l_run : 0.f;
+    const float inv = inv_with_sink(l_run, m_run, p.sink, my_head, p.out_scale);
 #pragma unroll
     for (int i = 0; i < AG_MAX_ACC; ++i)
       if (i < n_acc && sub + 8 * i < hdv) o[sub + 8 * i] = from_f32<T>(acc[i] * inv);
@@ -233,7 +244,8 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
                                     int page_size, int window, float scale, int act_dtype, const float* score_bias,
                                     int bias_dists, const float* head_scale, int hd_v, int keep_first,
-                                    float out_scale, int chunk, int n_v_heads, int v_row, cudaStream_t stream) {
+                                    float out_scale, int chunk, int n_v_heads, int v_row, const float* sink,
+                                    cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if (hd_v <= 0) hd_v = hd;
   if (hd <= 0 || hd > 8 * AG_MAX_ACC || hd_v > 8 * AG_MAX_ACC) return IE_BAD_SIZE;
@@ -243,7 +255,7 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
   if (v_row <= 0) v_row = hd_v;
   if (n_kv_heads % n_v_heads || v_row < hd_v || chunk < 0 || (chunk > 0 && keep_first > 0)) return IE_BAD_SIZE;
   AttnGeneralParams p;
-  p.chunk = chunk; p.n_v_heads = n_v_heads; p.v_row = v_row;
+  p.chunk = chunk; p.n_v_heads = n_v_heads; p.v_row = v_row; p.sink = sink;
   p.q = q; p.out = out; p.kpool = kpool; p.vpool = vpool; p.block_table = block_table;
   p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = work_req; p.work_pair0 = work_pair0;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
@@ -407,7 +419,7 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
   float l_all = 0.f;
 #pragma unroll
   for (int w = 0; w < AR_WARPS; ++w) l_all += s_m[w] == -INFINITY ? 0.f : s_l[w] * expf(s_m[w] - m_all);
-  const float inv = l_all > 0.f ? p.out_scale / l_all : 0.f;
+  const float inv = inv_with_sink(l_all, m_all, p.sink, head, p.out_scale);
   T* o = (T*)p.out + (size_t)n * p.out_stride + head * hdv;
   for (int d = threadIdx.x; d < hdv; d += AR_WARPS * 32) {
     float total = 0.f;
@@ -423,7 +435,7 @@ extern "C" int ie_attention_rows(const void* q, void* out, const void* kpool, co
                                  int n_tokens, int n_requests, int max_rows, int n_heads, int n_kv_heads, int hd,
                                  int page_size, int window, float scale, int act_dtype, const float* score_bias,
                                  int bias_dists, const float* head_scale, int hd_v, int keep_first, float out_scale,
-                                 int chunk, int n_v_heads, int v_row, cudaStream_t stream) {
+                                 int chunk, int n_v_heads, int v_row, const float* sink, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return IE_OK;
   if (hd_v <= 0) hd_v = hd;
   if (hd <= 0 || hd > 32 * AR_MAX_PER_LANE || hd_v > 32 * AR_MAX_PER_LANE) return IE_BAD_SIZE;
@@ -433,7 +445,7 @@ extern "C" int ie_attention_rows(const void* q, void* out, const void* kpool, co
   if (v_row <= 0) v_row = hd_v;
   if (n_kv_heads % n_v_heads || v_row < hd_v || chunk < 0 || (chunk > 0 && keep_first > 0)) return IE_BAD_SIZE;
   AttnGeneralParams p;
-  p.chunk = chunk; p.n_v_heads = n_v_heads; p.v_row = v_row;
+  p.chunk = chunk; p.n_v_heads = n_v_heads; p.v_row = v_row; p.sink = sink;
   p.q = q; p.out = out; p.kpool = kpool; p.vpool = vpool; p.block_table = block_table;
   p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = nullptr; p.work_pair0 = nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;

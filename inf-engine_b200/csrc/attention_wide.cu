@@ -56,6 +56,7 @@ struct WideParams {
   // n_splits > 1: block z takes the keys [first + z * split_keys, first + (z + 1) * split_keys) of its tile's range
   // (split_keys a multiple of the key tile) and leaves sums, maxima and unnormalised outputs for the merge kernel
   int n_splits, split_keys;
+  const float* sink;  // [n_heads] or null: the denominator of head h also holds exp(sink[h]) (no key, no value, not scaled)
   float* part_o;   // [blocks x, key heads, splits, BM, DV]
   float* part_ml;  // [blocks x, key heads, splits, BM, 2]
 };
@@ -121,6 +122,15 @@ __device__ __forceinline__ void load_tile(const WideParams& p, bf16* Ks, bf16* V
     else
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
   }
+}
+
+// 1 / (l + the sink's term) for a row whose sum l was formed at the maximum m (both in the exponent's base-2 units)
+__device__ __forceinline__ float wide_inv(float l, float m, const float* sink, int head) {
+  if (sink == nullptr || m == -INFINITY) return l > 0.f ? 1.f / l : 0.f;
+  const float sk = sink[head] * LOG2E;
+  const float m2 = fmaxf(m, sk);
+  const float f = exp2f(m - m2);
+  return f / (l * f + exp2f(sk - m2));
 }
 
 __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
@@ -314,8 +324,8 @@ __global__ void __launch_bounds__(THREADS) attention_wide_kernel(WideParams p) {
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     if (pr_[h] >= n_pairs) continue;
-    const float inv = l > 0.f ? 1.f / l : 0.f;
     const int t = pr_[h] / group, j = pr_[h] - t * group;
+    const float inv = wide_inv(l, m_run[h], p.sink, c * group + j);
     bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + (size_t)(c * group + j) * DV + 2 * t4;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
@@ -369,9 +379,9 @@ __global__ void __launch_bounds__(THREADS) attention_wide_merge_kernel(WideParam
       }
     }
   }
-  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
   const int pr = pair0 + r;
   const int t = pr / group, j = pr - t * group;
+  const float inv = wide_inv(l_all, m_all, p.sink, c * group + j);
   bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + (size_t)(c * group + j) * DV;
 #pragma unroll
   for (int i = 0; i < MERGE_SLOTS; ++i) {
@@ -389,7 +399,8 @@ extern "C" int ie_attention_wide_keys() { return BN; }
 
 static int wide_params(WideParams& p, const void* q, void* out, const void* kpool, const void* vpool, const int* block_table,
                        const int* q_start, const int* ctx_before, int q_stride, int out_stride, int table_stride, int n_heads,
-                       int n_kv_heads, int page_size, int window, float scale, int chunk, int n_v_heads, int v_row) {
+                       int n_kv_heads, int page_size, int window, float scale, int chunk, int n_v_heads, int v_row,
+                       const float* sink) {
   if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || window < 0 || chunk < 0) return IE_BAD_SIZE;
   if (n_v_heads <= 0) n_v_heads = n_kv_heads;
   if (v_row <= 0) v_row = DV;
@@ -402,7 +413,7 @@ static int wide_params(WideParams& p, const void* q, void* out, const void* kpoo
   p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = nullptr; p.work_pair0 = nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window; p.chunk = chunk;
-  p.n_v_heads = n_v_heads; p.v_row = v_row;
+  p.n_v_heads = n_v_heads; p.v_row = v_row; p.sink = sink;
   p.alias = (vpool == kpool && v_row == DK && n_v_heads == n_kv_heads && DV <= DK) ? 1 : 0;
   p.scale_log2 = scale * LOG2E;
   p.tiles = 1; p.max_rows = 0; p.n_splits = 1; p.split_keys = 0; p.part_o = nullptr; p.part_ml = nullptr;
@@ -417,12 +428,12 @@ extern "C" int ie_attention_wide(const void* q, void* out, const void* kpool, co
                                  const int* q_start, const int* ctx_before, const int* work_req, const int* work_pair0,
                                  int q_stride, int out_stride, int table_stride, int n_work, int n_heads, int n_kv_heads,
                                  int page_size, int window, float scale, int chunk, int n_v_heads, int v_row,
-                                 cudaStream_t stream) {
+                                 const float* sink, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if (work_req == nullptr || work_pair0 == nullptr) return IE_BAD_SIZE;
   WideParams p;
   const int rc = wide_params(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride,
-                             n_heads, n_kv_heads, page_size, window, scale, chunk, n_v_heads, v_row);
+                             n_heads, n_kv_heads, page_size, window, scale, chunk, n_v_heads, v_row, sink);
   if (rc != IE_OK) return rc;
   p.work_req = work_req; p.work_pair0 = work_pair0;
   const size_t smem = wide_smem(p);
@@ -445,13 +456,14 @@ extern "C" int ie_attention_wide_small(const void* q, void* out, const void* kpo
                                        const int* q_start, const int* ctx_before, int q_stride, int out_stride,
                                        int table_stride, int n_requests, int max_rows, int n_heads, int n_kv_heads,
                                        int page_size, int window, float scale, int chunk, int n_v_heads, int v_row,
-                                       int n_splits, int split_keys, float* scratch, cudaStream_t stream) {
+                                       int n_splits, int split_keys, float* scratch, const float* sink,
+                                       cudaStream_t stream) {
   if (n_requests <= 0) return IE_OK;
   if (max_rows <= 0 || n_splits <= 0 || n_splits > 65535) return IE_BAD_SIZE;
   if (n_splits > 1 && (split_keys <= 0 || split_keys % BN || scratch == nullptr)) return IE_BAD_SIZE;
   WideParams p;
   const int rc = wide_params(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride,
-                             n_heads, n_kv_heads, page_size, window, scale, chunk, n_v_heads, v_row);
+                             n_heads, n_kv_heads, page_size, window, scale, chunk, n_v_heads, v_row, sink);
   if (rc != IE_OK) return rc;
   p.tiles = (max_rows + BM - 1) / BM; p.max_rows = max_rows; p.n_splits = n_splits; p.split_keys = split_keys;
   const size_t n_parts = (size_t)n_requests * p.tiles * n_kv_heads * n_splits;

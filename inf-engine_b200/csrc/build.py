@@ -33,7 +33,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 # name -> sources; the headers every library depends on
 LIBRARIES = {
     "core": ["elementwise.cu", "rowwise.cu", "sequence.cu", "routed.cu", "attention_general.cu", "gemm_simt.cu",
-             "sampling.cu", "headwise.cu", "gating.cu"],
+             "sampling.cu", "headwise.cu", "gating.cu", "stream_shift.cu", "headmix.cu", "matrix_memory.cu"],
 }
 HEADERS = ["common.cuh"]
 

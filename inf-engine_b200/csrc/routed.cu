@@ -1,7 +1,7 @@
 // A mixture of feed-forward experts on the device, without a trip to the host:
 //   route    per token, from float32 router logits: sigmoid scores, a correction added for the choice only, the best
 //            groups of neighbouring experts kept, the top experts among them, their normalised weights, and the
-//            shared expert's gate;
+//            shared expert's gate; or (mode 1) the largest logits, a bias added, and the softmax over those alone;
 //   sort     the (token, choice) pairs ordered by expert, and a table of row tiles, none of which spans two experts;
 //   product  C[pair] = A[token of pair] W[expert of pair]^T over those tiles, optionally with silu(gate) * up in the
 //            epilogue: on CUDA cores (float32 products and sums, every output one accumulator that walks k upward) for
@@ -17,7 +17,7 @@ template <typename TW>
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ logits, int ld, const TW* __restrict__ correction, int* __restrict__ ids,
              float* __restrict__ weights, float* __restrict__ gate, int n_tokens, int n_experts, int top, int n_groups,
-             int keep_groups, float route_scale, float weight_eps, int gate_col) {
+             int keep_groups, float route_scale, float weight_eps, int gate_col, int mode) {
   extern __shared__ float sm[];
   pdl_trigger();
   pdl_wait();
@@ -29,9 +29,11 @@ route_kernel(const float* __restrict__ logits, int ld, const TW* __restrict__ co
   float* gscore = choice + n_experts;
   const float* z = logits + (size_t)t * ld;
   for (int e = lane; e < n_experts; e += 32) {
-    const float s = 1.f / (1.f + expf(-z[e]));
+    const float cor = correction ? to_f32(correction[e]) : 0.f;
+    // mode 1: the logits themselves (plus their bias) are both what is compared and what the weights are made of
+    const float s = mode == 1 ? z[e] + cor : 1.f / (1.f + expf(-z[e]));
     score[e] = s;
-    choice[e] = s + (correction ? to_f32(correction[e]) : 0.f);
+    choice[e] = mode == 1 ? s : s + cor;
   }
   __syncwarp();
   const int per = n_experts / n_groups;
@@ -90,6 +92,18 @@ route_kernel(const float* __restrict__ logits, int ld, const TW* __restrict__ co
     }
     __syncwarp();
   }
+  if (lane == 0 && mode == 1) {
+    // softmax over the chosen logits alone; the first chosen is the largest
+    const float top0 = weights[(size_t)t * top];
+    float sum = 0.f;
+    for (int r = 0; r < top; ++r) {
+      const float e = expf(weights[(size_t)t * top + r] - top0);
+      weights[(size_t)t * top + r] = e;
+      sum += e;
+    }
+    total = sum;
+    weight_eps = 0.f;
+  }
   if (lane == 0) {
     const float f = route_scale / (total + weight_eps);
     for (int r = 0; r < top; ++r) weights[(size_t)t * top + r] *= f;
@@ -99,7 +113,7 @@ route_kernel(const float* __restrict__ logits, int ld, const TW* __restrict__ co
 
 extern "C" int ie_moe_route(const float* logits, int ld, const void* correction, int w_dtype, int* ids, float* weights,
                             float* gate, int n_tokens, int n_experts, int top, int n_groups, int keep_groups,
-                            float route_scale, float weight_eps, int gate_col, cudaStream_t stream) {
+                            float route_scale, float weight_eps, int gate_col, int mode, cudaStream_t stream) {
   if (n_tokens <= 0) return IE_OK;
   if (n_experts <= 0 || top <= 0 || top > n_experts || n_groups <= 0 || n_experts % n_groups || keep_groups <= 0 ||
       keep_groups > n_groups)
@@ -109,10 +123,10 @@ extern "C" int ie_moe_route(const float* logits, int ld, const void* correction,
   const unsigned blocks = (unsigned)((n_tokens + 3) / 4);
   if (w_dtype == IE_F32)
     return launch_k(route_kernel<float>, blocks, 128, smem, stream, logits, ld, (const float*)correction, ids, weights,
-                    gate, n_tokens, n_experts, top, n_groups, keep_groups, route_scale, weight_eps, gate_col);
+                    gate, n_tokens, n_experts, top, n_groups, keep_groups, route_scale, weight_eps, gate_col, mode);
   if (w_dtype == IE_BF16)
     return launch_k(route_kernel<bf16>, blocks, 128, smem, stream, logits, ld, (const bf16*)correction, ids, weights,
-                    gate, n_tokens, n_experts, top, n_groups, keep_groups, route_scale, weight_eps, gate_col);
+                    gate, n_tokens, n_experts, top, n_groups, keep_groups, route_scale, weight_eps, gate_col, mode);
   return IE_BAD_DTYPE;
 }
 

@@ -80,7 +80,7 @@ def core():
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, I, P]
-        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P]
+        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P, P]
         lib.ie_layernorm.argtypes = [P, P, P, P, I, P, I, P, I, I, F, P]
         lib.ie_embed_bigram.argtypes = [P, P, P, P, I, P, P, I, P, P, I, I, I, I, L, L, P]
         lib.ie_add_bias.argtypes = [P, I, P, I, I, I, I, P]
@@ -93,10 +93,10 @@ def core():
         lib.ie_cast_rows.argtypes = [P, P, I, I, I, P]
         lib.ie_outnorm_accumulate.argtypes = [P, P, I, I, P, I, P, I, I, I, F, P]
         lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, I, P]
-        lib.ie_attention_rows.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P]
+        lib.ie_attention_rows.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P, P]
         lib.ie_linear_recurrence.argtypes = [P, I, P, I, P, P, I, P, P, P, I, P, P, I, P, P, I, I, F, F, I, I, P]
         lib.ie_rownorm_rotate_write.argtypes = [P, P, P, I, I, I, P, P, P, P, P, I, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
-        lib.ie_moe_route.argtypes = [P, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P]
+        lib.ie_moe_route.argtypes = [P, I, P, I, P, P, P, I, I, I, I, I, F, F, I, I, P]
         lib.ie_moe_sort.argtypes = [P, I, I, I, P, P, I, P]
         lib.ie_moe_gemm.argtypes = [P, I, P, I, P, I, P, P, I, I, I, I, I, L, I, I, I, I, P]
         lib.ie_moe_combine.argtypes = [P, P, P, P, I, I, P, I, I, I, P]
@@ -109,6 +109,18 @@ def core():
         lib.ie_glu_act.argtypes = [P, P, I, I, I, I, I, F, F, F, I, P]
         lib.ie_mingru_scan.argtypes = [P, P, I, P, I, P, P, I, P, P, I, P, P, I, I, I, I, P]
         lib.ie_mingru_scan_hint.argtypes = [P, P, I, P, I, P, P, I, P, P, I, P, P, I, I, I, I, I, P]
+        D = ctypes.c_double
+        lib.ie_scale_add_sinusoid.argtypes = [P, P, F, D, I, I, P]
+        lib.ie_add_row.argtypes = [P, P, I, I, I, P]
+        lib.ie_token_shift.argtypes = [P, P, I, P, I, P, P, P, P, I, I, I, I, P]
+        lib.ie_gate_mul.argtypes = [P, I, P, I, I, I, I, I, P]
+        lib.ie_qkv_prepare.argtypes = [P, I, I, P, I, P, I, I, P, I, I, P, I, I, I, P, I, I, F, P, P, P, I, I, I, I, P]
+        lib.ie_talk_combine.argtypes = [P, I, P, P, I, P, I, I, I, I, I, I, I, I, P]
+        lib.ie_mlstm_scan.argtypes = [P, P, P, I, I, I, P, P, I, P, P, I, F, F, P, L, P, I, P, P, I, I, I, I, I, I, P]
+        lib.ie_mlstm_finish.argtypes = [P, I, P, I, P, I, P, I, I, I, I, F, I, P]
+        lib.ie_mlstm_chunks.argtypes = [I, I]
+        lib.ie_mlstm_state_floats.argtypes = [I, I]
+        lib.ie_mlstm_state_floats.restype = c_longlong
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
         lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
         lib.ie_sample.argtypes = [P, P, P, I, I, L, P]
@@ -119,7 +131,9 @@ def core():
                      "ie_causal_conv", "ie_linear_recurrence", "ie_rownorm_rotate_write", "ie_moe_route", "ie_moe_sort",
                      "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows", "ie_gemm_rowdot", "ie_head_prepare",
                      "ie_heads_gemm", "ie_diff_combine", "ie_gated_residual_add", "ie_scale_rows", "ie_glu_act",
-                     "ie_mingru_scan", "ie_mingru_scan_hint"):
+                     "ie_mingru_scan", "ie_mingru_scan_hint", "ie_scale_add_sinusoid", "ie_add_row", "ie_token_shift",
+                     "ie_gate_mul", "ie_qkv_prepare", "ie_talk_combine", "ie_mlstm_scan", "ie_mlstm_finish",
+                     "ie_mlstm_chunks"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -275,14 +289,17 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                       n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
                       score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
                       v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0, chunk: int = 0,
-                      n_v_heads: int | None = None, v_row: int | None = None) -> None:
+                      n_v_heads: int | None = None, v_row: int | None = None, sink: torch.Tensor | None = None) -> None:
     """Paged causal attention in float32 arithmetic.  ``score_bias`` (float32 [n_heads, D], contiguous) is added to
     the scaled score of a query at position p and a key at position j as ``score_bias[head, min(p - j, D - 1)]``.
     ``head_scale`` (float32 [n_heads]) multiplies the score of its head beside ``scale``.  ``v_head_dim``: head size of
     the values and of ``out`` when it is not ``head_dim``.  ``keep_first``: beside a window, keys at positions below it
     stay visible to every later query.  ``out_scale`` multiplies the output.  ``chunk``: a query sees only the keys of
     its own chunk of that many positions.  ``n_v_heads``: heads of the value pool when several key heads share a value
-    head; ``v_row``: elements between value rows when the values are the first dimensions of the key rows (one pool)."""
+    head; ``v_row``: elements between value rows when the values are the first dimensions of the key rows (one pool).
+    ``sink`` (float32 [n_heads]): the softmax's denominator of head h also holds exp(sink[h]), a term without a key or
+    a value that ``scale`` does not touch."""
+    assert sink is None or (sink.dtype is torch.float32 and sink.is_contiguous() and sink.shape == (n_heads,))
     assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     if score_bias is not None:
@@ -296,7 +313,7 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                                        dtype_code(q.dtype), _ptr(score_bias),
                                        score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
                                        int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale),
-                                       int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
+                                       int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _ptr(sink), _stream()),
            f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -305,7 +322,7 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpoo
                    n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
                    score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
                    v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0, chunk: int = 0,
-                   n_v_heads: int | None = None, v_row: int | None = None) -> None:
+                   n_v_heads: int | None = None, v_row: int | None = None, sink: torch.Tensor | None = None) -> None:
     """``attention_general`` for the requests of the step that bring at most ``max_rows`` (token, head-in-group) rows
     (decode tokens, as a rule): a block per (token, query head) whose warps split the visible keys.  Rows of requests
     that bring more are left untouched (the tile kernel's, with a work list of those requests)."""
@@ -321,7 +338,7 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpoo
                                     float(scale), dtype_code(q.dtype), _ptr(score_bias),
                                     score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
                                     int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale),
-                                    int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
+                                    int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _ptr(sink), _stream()),
            f"attention_rows(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -559,6 +576,124 @@ def mingru_scan(z_pre: torch.Tensor, u_pre: torch.Tensor, g_pre: torch.Tensor, z
                                       dtype_code(out.dtype), int(max_q_len or 0), _stream()), f"mingru_scan(width={width})")
 
 
+# ------------------------------------------------- the stream, shifted inputs, mixed heads, the matrix memory
+def scale_add_sinusoid(x: torch.Tensor, positions: torch.Tensor, scale: float, base: float) -> None:
+    """x (float32 [n, d]) <- x * scale + s(position): s[2i] = sin(p base^(-2i / d)), s[2i + 1] the cosine of the same."""
+    assert x.dtype is torch.float32 and x.is_contiguous() and positions.dtype is torch.int32
+    _check(core().ie_scale_add_sinusoid(_ptr(x), _ptr(positions), float(scale), float(base), x.shape[0], x.shape[1],
+                                        _stream()), "scale_add_sinusoid")
+
+
+def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
+    """x (float32 [n, d]) += row ([d]) for every row of x."""
+    assert x.dtype is torch.float32 and x.is_contiguous() and row.is_contiguous() and row.shape == (x.shape[1],)
+    _check(core().ie_add_row(_ptr(x), _ptr(row), dtype_code(row.dtype), x.shape[0], x.shape[1], _stream()), "add_row")
+
+
+def token_shift(h: torch.Tensor, out: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+                ctx_before: torch.Tensor, slots: torch.Tensor, n_requests: int, write_state: bool = True) -> None:
+    """out = h + (h' - h) * mu with h' the row of the token before (as it was), zeros before a sequence's first token;
+    ``state`` [slots, d] (of h's type) carries a request's last row from step to step."""
+    n, d = h.shape
+    assert h.is_contiguous() and out.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype
+    assert out.data_ptr() != h.data_ptr() and mu.shape == (d,) and mu.is_contiguous()
+    assert state.dtype == h.dtype and state.is_contiguous() and state.shape[1:] == (d,)
+    _check(core().ie_token_shift(_ptr(h), _ptr(out), dtype_code(h.dtype), _ptr(mu), dtype_code(mu.dtype), _ptr(state),
+                                 _ptr(q_start), _ptr(ctx_before), _ptr(slots), n_requests, n, d, 1 if write_state else 0,
+                                 _stream()), "token_shift")
+
+
+def gate_mul(x: torch.Tensor, gate_pre: torch.Tensor, group: int = 1) -> None:
+    """x[n, j] *= sigmoid(gate_pre[n, j // group]) in place: a gate per coordinate, or per head of ``group`` coordinates."""
+    n, d = x.shape
+    assert x.stride(1) == 1 and gate_pre.stride(1) == 1 and gate_pre.dtype == x.dtype and gate_pre.shape == (n, d // group)
+    _check(core().ie_gate_mul(_ptr(x), x.stride(0), _ptr(gate_pre), gate_pre.stride(0), n, d, int(group),
+                              dtype_code(x.dtype), _stream()), "gate_mul")
+
+
+def qkv_prepare(q: torch.Tensor, q_heads: int, k: torch.Tensor, k_heads: int, head_dim: int, v: torch.Tensor, v_heads: int,
+                v_head_dim: int, slot_mapping: torch.Tensor | None, kpool: torch.Tensor | None, vpool: torch.Tensor | None,
+                page_size: int, eps: float, q_bias=None, k_bias=None, v_bias=None, q_norm: bool = False,
+                k_norm: bool = False, v_norm: bool = False, pool_v_heads: int | None = None) -> None:
+    """Per token: biases added to q, k and v, every head of a side whose flag is set divided by its root mean square
+    (no gain), q written back in place, k to its slot of ``kpool`` [pages, k_heads, page_size, head_dim] and v to
+    ``vpool`` [pages, pool_v_heads, page_size, v_heads * v_head_dim / pool_v_heads]."""
+    n = q.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
+    biases = [b for b in (q_bias, k_bias, v_bias) if b is not None]
+    assert all(b.dtype == biases[0].dtype and b.is_contiguous() for b in biases)
+    assert q_bias is None or q_bias.numel() == q_heads * head_dim
+    assert k_bias is None or k_bias.numel() == k_heads * head_dim
+    assert v_bias is None or v_bias.numel() == v_heads * v_head_dim
+    assert (kpool is None or kpool.dtype == q.dtype) and (vpool is None or vpool.dtype == q.dtype)
+    _check(core().ie_qkv_prepare(_ptr(q), q.stride(0), q_heads, _ptr(q_bias), 1 if q_norm else 0, _ptr(k), k.stride(0),
+                                 k_heads, _ptr(k_bias), 1 if k_norm else 0, head_dim, _ptr(v), v.stride(0), v_heads,
+                                 v_head_dim, _ptr(v_bias), 1 if v_norm else 0,
+                                 dtype_code(biases[0].dtype) if biases else IE_F32, float(eps), _ptr(slot_mapping),
+                                 _ptr(kpool), _ptr(vpool), int(pool_v_heads or v_heads), n, page_size,
+                                 dtype_code(q.dtype), _stream()), "qkv_prepare")
+
+
+def talk_combine(a: torch.Tensor, talk: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, n_heads: int,
+                 n_v_heads: int, v_head_dim: int, first_v_head: int = 0, slice_v_heads: int | None = None) -> None:
+    """``out[n, h] = sum_g talk[h, g] * a[n, g, value head of h] * sigmoid(gate[n, h])``: ``a`` [n, n_heads *
+    slice_v_heads * v_head_dim] holds every query head's softmax weights applied to the value heads first_v_head ..
+    first_v_head + slice_v_heads - 1; the heads of ``out`` ([n, n_heads * v_head_dim]) that read those are written."""
+    n = out.shape[0]
+    nc = int(slice_v_heads or n_v_heads)
+    assert a.stride(1) == 1 and out.stride(1) == 1 and a.dtype == out.dtype and a.shape[1] == n_heads * nc * v_head_dim
+    assert talk.dtype is torch.float32 and talk.is_contiguous() and talk.shape == (n_heads, n_heads)
+    assert gate is None or (gate.stride(1) == 1 and gate.dtype == out.dtype and gate.shape == out.shape)
+    _check(core().ie_talk_combine(_ptr(a), a.stride(0), _ptr(talk), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                  _ptr(out), out.stride(0), n, n_heads, n_v_heads, v_head_dim, int(first_v_head), nc,
+                                  dtype_code(out.dtype), _stream()), "talk_combine")
+
+
+def mlstm_state_floats(head_dim: int, v_head_dim: int) -> int:
+    """float32 words of a head's state in ``mlstm_scan``: the matrix, and a copy of the normaliser and the maximum for
+    every chunk of value columns that a block takes."""
+    n = int(core().ie_mlstm_state_floats(int(head_dim), int(v_head_dim)))
+    if n <= 0:
+        raise KernelError(f"mlstm_scan takes no heads of {head_dim} x {v_head_dim}")
+    return n
+
+
+def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, i_bias: torch.Tensor,
+               f_bias: torch.Tensor, cap: float, state: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+               slots: torch.Tensor, n_requests: int, n_heads: int, head_dim: int, v_head_dim: int,
+               write_state: bool = True) -> None:
+    """The matrix memory with stabilised exponential gates over each request's tokens of the step.  ``gates`` float32
+    [n, 2 * n_heads]: the pre-activations of the input gates, then of the forget gates (biases added here); ``state``
+    float32 [slots, n_heads, mlstm_state_floats]; ``out`` float32 [n, n_heads * v_head_dim] takes S^T q over its
+    denominator, before the head norm."""
+    n = out.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
+    assert gates.dtype is torch.float32 and gates.stride(1) == 1 and gates.shape == (n, 2 * n_heads)
+    assert i_bias.dtype == f_bias.dtype and i_bias.is_contiguous() and f_bias.is_contiguous()
+    assert i_bias.shape == f_bias.shape == (n_heads,)
+    assert state.dtype is torch.float32 and state.is_contiguous()
+    assert state.shape[1:] == (n_heads, mlstm_state_floats(head_dim, v_head_dim))
+    assert out.dtype is torch.float32 and out.stride(1) == 1 and out.shape[1] == n_heads * v_head_dim
+    _check(core().ie_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(gates),
+                                gates.data_ptr() + 4 * n_heads, gates.stride(0), _ptr(i_bias), _ptr(f_bias),
+                                dtype_code(i_bias.dtype), float(cap), float(head_dim) ** -0.5, _ptr(state),
+                                state.stride(0), _ptr(out), out.stride(0), _ptr(q_start), _ptr(slots), n_requests,
+                                n_heads, head_dim, v_head_dim, 1 if write_state else 0, dtype_code(q.dtype), _stream()),
+           f"mlstm_scan(heads={n_heads}, {head_dim} x {v_head_dim})")
+
+
+def mlstm_finish(o: torch.Tensor, gain: torch.Tensor, gate_pre: torch.Tensor, out: torch.Tensor, n_heads: int,
+                 v_head_dim: int, eps: float) -> None:
+    """out = o / rms(o over each head) * gain * sigmoid(gate_pre): ``o`` float32, ``gain`` of all heads' size."""
+    n = out.shape[0]
+    w = n_heads * v_head_dim
+    assert o.dtype is torch.float32 and o.stride(1) == 1 and o.shape == (n, w) and gain.is_contiguous() and gain.shape == (w,)
+    assert gate_pre.stride(1) == 1 and out.stride(1) == 1 and gate_pre.dtype == out.dtype and gate_pre.shape == (n, w)
+    _check(core().ie_mlstm_finish(_ptr(o), o.stride(0), _ptr(gain), dtype_code(gain.dtype), _ptr(gate_pre),
+                                  gate_pre.stride(0), _ptr(out), out.stride(0), n, n_heads, v_head_dim, float(eps),
+                                  dtype_code(out.dtype), _stream()), "mlstm_finish")
+
+
 # ------------------------------------------------------------------ a mixture of experts
 def moe_tile_rows() -> int:
     return int(core().ie_moe_tile_rows())
@@ -569,11 +704,17 @@ def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
     return -(-n_pairs // moe_tile_rows()) + min(n_experts, n_pairs)
 
 
+ROUTE_SCORES = {"sigmoid": 0, "softmax_top": 1}
+
+
 def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, ids: torch.Tensor, weights: torch.Tensor,
               gate: torch.Tensor | None, n_experts: int, top: int, n_groups: int, keep_groups: int, route_scale: float,
-              weight_eps: float, gate_col: int = -1) -> None:
+              weight_eps: float, gate_col: int = -1, score: str = "sigmoid") -> None:
     """Per token, from float32 router ``logits`` [n, >= n_experts]: the chosen experts ``ids`` int32 [n, top] and their
-    ``weights`` float32 [n, top]; ``gate`` float32 [n] = sigmoid(logits[:, gate_col]) (the shared expert's)."""
+    ``weights`` float32 [n, top]; ``gate`` float32 [n] = sigmoid(logits[:, gate_col]) (the shared expert's).  ``score``
+    "sigmoid": sigmoid scores, ``correction`` added for the choice only, weights the chosen scores over their sum.
+    "softmax_top": ``correction`` is a bias of the logits themselves, the largest ``top`` are chosen and their weights
+    are the softmax over the chosen logits alone (times ``route_scale``)."""
     n = logits.shape[0]
     assert logits.dtype is torch.float32 and logits.stride(1) == 1 and ids.dtype is torch.int32 and ids.is_contiguous()
     assert weights.dtype is torch.float32 and weights.is_contiguous() and ids.shape == weights.shape == (n, top)
@@ -581,7 +722,7 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, ids: torch.
     _check(core().ie_moe_route(_ptr(logits), logits.stride(0), _ptr(correction),
                                dtype_code(correction.dtype) if correction is not None else IE_F32, _ptr(ids),
                                _ptr(weights), _ptr(gate), n, n_experts, top, n_groups, keep_groups, float(route_scale),
-                               float(weight_eps), int(gate_col), _stream()), f"moe_route(experts={n_experts}, top={top})")
+                               float(weight_eps), int(gate_col), ROUTE_SCORES[score], _stream()), f"moe_route(experts={n_experts}, top={top})")
 
 
 def moe_sort(ids: torch.Tensor, n_experts: int, sorted_pairs: torch.Tensor, tiles: torch.Tensor) -> None:
@@ -755,11 +896,11 @@ def attention_wide_library(head_dim: int, v_head_dim: int):
         defines = {"IE_AW_DK": key[0], "IE_AW_DV": key[1], **BUILD_DEFINES.get("attn_wide", {})}
         lib = load_library(f"attn_wide_k{key[0]}_v{key[1]}", ["attention_wide.cu"], defines)
         P, I, F = c_void_p, c_int, c_float
-        lib.ie_attention_wide.argtypes = [P] * 9 + [I] * 8 + [F, I, I, I, P]
+        lib.ie_attention_wide.argtypes = [P] * 9 + [I] * 8 + [F, I, I, I, P, P]
         lib.ie_attention_wide.restype = c_int
         lib.ie_attention_wide_rows.restype = c_int
         lib.ie_attention_wide_keys.restype = c_int
-        lib.ie_attention_wide_small.argtypes = [P] * 7 + [I] * 9 + [F] + [I] * 5 + [P, P]
+        lib.ie_attention_wide_small.argtypes = [P] * 7 + [I] * 9 + [F] + [I] * 5 + [P, P, P]
         lib.ie_attention_wide_small.restype = c_int
         lib.ie_attention_wide_small_scratch.argtypes = [I, I, I, I]
         lib.ie_attention_wide_small_scratch.restype = c_longlong
@@ -773,7 +914,7 @@ ATTENTION_WIDE_ROWS = 64     # (token, head-in-group) pairs of a tile of the ker
 
 def attention_wide(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work, n_heads,
                    n_kv_heads, head_dim, page_size, window, scale, v_head_dim: int | None = None, chunk: int = 0,
-                   n_v_heads: int | None = None, v_row: int | None = None) -> None:
+                   n_v_heads: int | None = None, v_row: int | None = None, sink: torch.Tensor | None = None) -> None:
     """Causal paged attention of prompt portions on tensor cores with float32 scores, maxima and sums, the weights to
     two bfloat16 terms: ``attention_general``'s options ``v_head_dim``, ``chunk``, ``n_v_heads`` and ``v_row`` and a
     window, for bfloat16 operands whose head sizes are multiples of 16.  The work list cuts each request's (token,
@@ -785,7 +926,7 @@ def attention_wide(q, out, kpool, vpool, block_table, q_start, ctx_before, work_
     _check(lib.ie_attention_wide(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
                                  _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0),
                                  block_table.stride(0), n_work, n_heads, n_kv_heads, page_size, int(window or 0),
-                                 float(scale), int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _stream()),
+                                 float(scale), int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), _ptr(sink), _stream()),
            f"attention_wide(head_dim={head_dim}/{dv}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -809,7 +950,7 @@ def attention_wide_small_scratch(head_dim: int, v_head_dim: int, n_requests: int
 def attention_wide_small(q, out, kpool, vpool, block_table, q_start, ctx_before, n_requests: int, max_rows: int, n_heads,
                          n_kv_heads, head_dim, page_size, window, scale, n_splits: int, split_keys: int,
                          scratch: torch.Tensor | None, v_head_dim: int | None = None, chunk: int = 0,
-                         n_v_heads: int | None = None, v_row: int | None = None) -> None:
+                         n_v_heads: int | None = None, v_row: int | None = None, sink: torch.Tensor | None = None) -> None:
     """``attention_wide`` for the requests of the step that bring at most ``max_rows`` (token, head-in-group) rows (decode
     tokens, as a rule), without a work list: every (request, key head) is cut into ``n_splits`` runs of ``split_keys``
     keys (``attention_wide_splits``), a block each, and a second kernel merges them through ``scratch`` (float32,
@@ -825,7 +966,7 @@ def attention_wide_small(q, out, kpool, vpool, block_table, q_start, ctx_before,
                                        _ptr(ctx_before), q.stride(0), out.stride(0), block_table.stride(0), n_requests,
                                        int(max_rows), n_heads, n_kv_heads, page_size, int(window or 0), float(scale),
                                        int(chunk or 0), int(n_v_heads or 0), int(v_row or 0), int(n_splits), int(split_keys),
-                                       _ptr(scratch), _stream()),
+                                       _ptr(scratch), _ptr(sink), _stream()),
            f"attention_wide_small(head_dim={head_dim}/{dv}, heads={n_heads}/{n_kv_heads}, splits={n_splits})")
     if n_splits > 1:
         global LAUNCHES
@@ -1192,7 +1333,8 @@ def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, wo
 # (the device has no sanitizer here: this is what stands in for one while debugging a cache manager or a new part)
 CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "attn_wide", "delta_rule", "gated_delta")
 CHECK_UNITS = ("elementwise", "rowwise", "sequence", "attention_general", "attention_mma", "attention_tcgen05",
-               "attention_wide", "delta_rule", "gated_delta", "headwise", "gating")
+               "attention_wide", "delta_rule", "gated_delta", "headwise", "gating", "stream_shift", "headmix",
+               "matrix_memory")
 CHECK_CODES = {1: "page id", 2: "cache slot", 3: "token id"}
 _check_limits: tuple[int, int, int] | None = None
 

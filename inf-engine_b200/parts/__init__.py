@@ -1,12 +1,13 @@
-from . import attention, block, delta_rule, feedforward, gated_delta, latent, model, norms, positions, recurrence, routed  # noqa: F401  (register the built-in parts)
+from . import attention, block, delta_rule, feedforward, gated_delta, latent, matrix_memory, model, norms, positions, recurrence, routed, talking  # noqa: F401  (register the built-in parts)
 from .attention import CacheView, PagedAttention
-from .block import GatedPreNormBlock, OutputNormBlock, PreNormBlock
+from .block import GatedPreNormBlock, OutputNormBlock, PreNormBlock, SandwichBlock
 from .delta_rule import GeneralDeltaMixer
 from .feedforward import GatedMLP, PolyNormMLP
 from .gated_delta import GatedDeltaMixer
 from .latent import DifferentialAttention, LatentAttention
 from .linear import Linear
-from .model import BigramDecoderModel, DecoderModel, ReinjectDecoderModel
+from .matrix_memory import MatrixMemory
+from .model import BigramDecoderModel, DecoderModel, PassOffsetDecoderModel, ReinjectDecoderModel
 from .norms import LayerNorm, RMSNorm
 from .positions import BucketedBias, NoPosition, PartialRotation, Rotary, RotaryPairs, distance_bucket, rotary_inv_freq, rotary_tables
 from .recurrence import GatedLinearRecurrence, MinGRU, ParallelMixer
@@ -26,4 +27,5 @@ from .registry import (
     register_position,
 )
 from .routed import RoutedExperts
+from .talking import TalkingAttention
 from .runtime import Runtime, Staging, Workspace

@@ -1,5 +1,6 @@
-"""The pre-norm residual block: ``x += mixer(norm(x)); x += ff(norm(x))``
-(engine/llama_block.py:50-62).  The sums are folded into the norm that follows
+"""Residual blocks.  The pre-norm block: ``x += mixer(norm(x)); x += ff(norm(x))``
+(engine/llama_block.py:50-62); beside it a block that norms its sublayers' outputs, a pre-norm block with gates per
+coordinate, and a block with a norm before and after each sublayer whose mixer may read shifted inputs.  The sums are folded into the norm that follows
 them: a block hands on the residual and a delta that is not added yet.  A block
 whose spec has no feed-forward is the first half alone."""
 
@@ -203,6 +204,77 @@ class GatedPreNormBlock:
         if self.feedforward is not None:
             h = self.ff_norm.add_norm(residual, None)
             self._add(residual, self.feedforward.forward(h, ctx), h, self.ff_gate, self.ff_gate_bias)
+        return residual, None
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """``x += out_norm1(mixer(shift(norm1(x))))``, then ``x += out_norm2(ff(norm2(x)))``: a norm before and a norm after
+    each sublayer.  ``shift`` (optional) replaces what the mixer reads, h, by ``h + (h' - h) * mu`` with h' the h of the
+    token before and mu a learned vector; the last h of every request is state of the run, kept beside the mixer's own
+    cache (the run's requirement is then the pair, the mixer's first).  The residual is float32; the norm after a
+    sublayer and the sum into the residual are one kernel."""
+
+    @staticmethod
+    def expected_tensors(spec):
+        out = {}
+        out.update(norm_class(spec.mixer_norm).expected_tensors(spec.mixer_norm))
+        if spec.feedforward is not None:
+            out.update(norm_class(spec.ff_norm).expected_tensors(spec.ff_norm))
+        out.update(norm_class(spec.mixer_out_norm).expected_tensors(spec.mixer_out_norm))
+        if spec.feedforward is not None:
+            out.update(norm_class(spec.ff_out_norm).expected_tensors(spec.ff_out_norm))
+        out.update(mixer_class(spec.mixer).expected_tensors(spec.mixer))
+        if spec.feedforward is not None:
+            out.update(feedforward_class(spec.feedforward).expected_tensors(spec.feedforward))
+        if spec.token_shift is not None:
+            out[spec.token_shift] = ExpectedTensor((spec.mixer_norm.size,))
+        return out
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.rt = rt
+        self.mixer_norm = build_norm(spec.mixer_norm, tensors, rt)
+        self.mixer_out_norm = build_norm(spec.mixer_out_norm, tensors, rt)
+        self.mixer = build_mixer(spec.mixer, tensors, rt)
+        has_ff = spec.feedforward is not None
+        self.ff_norm = build_norm(spec.ff_norm, tensors, rt) if has_ff else None
+        self.ff_out_norm = build_norm(spec.ff_out_norm, tensors, rt) if has_ff else None
+        self.feedforward = build_feedforward(spec.feedforward, tensors, rt) if has_ff else None
+        for norm in (self.mixer_out_norm, self.ff_out_norm):
+            if norm is not None and not hasattr(norm, "accumulate"):
+                raise ValueError(f"the norm after a sublayer needs accumulate(); {type(norm).__name__} has none")
+        self.shift = tensors[spec.token_shift].contiguous() if spec.token_shift is not None else None
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feedforward) if p is not None)
+
+    def cache_requirement(self):
+        """The mixer's requirement, and beside it the last input row of every request when inputs are shifted."""
+        from ..cache.manager import CacheRequirement
+        own = self.mixer.cache_requirement()
+        if self.shift is None:
+            return own
+        last = CacheRequirement(kind="state", state_shape=(self.spec.mixer_norm.size,), state_dtype=self.rt.act_dtype)
+        return CacheRequirement(kind="several", parts=(own, last))
+
+    def forward(self, residual, pending, ctx, cache):
+        ctx.handover = None
+        ctx.upcoming_norm = None
+        ctx.residual_cast = None
+        h = self.mixer_norm.add_norm(residual, pending)
+        mixer_cache = cache
+        if self.shift is not None:
+            mixer_cache, last = cache.parts
+            shifted = self.rt.ws.take("shifted", tuple(h.shape), self.rt.act_dtype)
+            kernels.token_shift(h, shifted, self.shift, last.state, ctx.q_start, ctx.ctx_before, ctx.slots,
+                                ctx.n_requests, write_state=cache.write)
+            h = shifted
+        self.mixer_out_norm.accumulate(residual, self.mixer.forward(h, ctx, mixer_cache))
+        if self.feedforward is not None:
+            h = self.ff_norm.add_norm(residual, None)
+            self.ff_out_norm.accumulate(residual, self.feedforward.forward(h, ctx))
         return residual, None
 
 

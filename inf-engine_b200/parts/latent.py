@@ -25,7 +25,7 @@ import torch
 from .. import kernels
 from ..cache.manager import CacheRequirement
 from ..weights.loader import ExpectedTensor
-from .linear import Linear
+from .linear import Linear, stack_rows
 from .registry import build_position, position_class, register_mixer
 
 SMALL_REQUEST_TOKENS = 4      # requests that bring at most this many tokens get the split-key rows kernel
@@ -35,47 +35,52 @@ WIDE_SMALL_MIN_GROUP = 4      # query heads a key head from which decode tokens 
 
 
 def attend_float32(q, out, kpool, vpool, ctx, kvctx, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
-                   scale: float, chunk: int | None, n_v_heads: int | None = None, v_row: int | None = None) -> None:
+                   scale: float, chunk: int | None, n_v_heads: int | None = None, v_row: int | None = None,
+                   window: int | None = None, sink: torch.Tensor | None = None) -> None:
     """Causal attention of the step's queries over the paged keys with float32 scores, maxima, weights and sums.
     Requests of at most ``SMALL_REQUEST_TOKENS`` tokens (decode tokens): a block per (token, head) whose warps split the
     keys, or, in bfloat16 storage with head sizes that are multiples of 16 and several query heads a key head, the
     tensor-core kernel with the keys split over blocks (every key row is then loaded once for all those heads).  The
     others (prompt portions), through a work list: the tensor-core kernel under the same conditions, else the float32
-    tile kernel."""
+    tile kernel.  ``window``: a query sees itself and the window - 1 keys before it.  ``sink`` (float32 [n_heads]): a
+    term exp(sink_h) without key or value in the denominator of head h."""
     group = n_heads // n_kv_heads
     max_rows = SMALL_REQUEST_TOKENS * group
     if ctx.max_q_len <= SMALL_REQUEST_TOKENS:
         n_small = ctx.n_requests
     else:
         n_small = sum(1 for n in ctx.host["q_lens"] if n <= SMALL_REQUEST_TOKENS)
-    extra = dict(v_head_dim=v_head_dim, chunk=chunk or 0, n_v_heads=n_v_heads, v_row=v_row)
-    wide = kpool.dtype is torch.bfloat16 and kernels.attention_wide_supports(q, out, head_dim, v_head_dim, v_row)
+    extra = dict(v_head_dim=v_head_dim, chunk=chunk or 0, n_v_heads=n_v_heads, v_row=v_row, sink=sink)
+    wide = (kpool.dtype is torch.bfloat16 and kernels.attention_wide_supports(q, out, head_dim, v_head_dim, v_row)
+            and kpool.data_ptr() % 16 == 0 and vpool.data_ptr() % 16 == 0)
     if n_small:
         if wide and group >= WIDE_SMALL_MIN_GROUP:
             rows = kernels.ATTENTION_WIDE_ROWS
             # the longest run of keys a small request may see, from the tile boundary below its first key
             keys = min(ctx.keys_cap, chunk + SMALL_REQUEST_TOKENS) if chunk else ctx.keys_cap
+            if window:
+                keys = min(keys, window + SMALL_REQUEST_TOKENS)
             n_splits, split_keys = kernels.attention_wide_splits(head_dim, v_head_dim, keys + 64,
                                                                   ctx.n_requests * -(-max_rows // rows) * n_kv_heads)
             words = kernels.attention_wide_small_scratch(head_dim, v_head_dim, ctx.n_requests, max_rows, n_kv_heads, n_splits)
             scratch = ctx.rt.ws.take("attn_wide_scratch", (words,), torch.float32) if words else None
             kernels.attention_wide_small(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, ctx.n_requests,
-                                         max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, n_splits,
+                                         max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, window, scale, n_splits,
                                          split_keys, scratch, **extra)
         else:
             kernels.attention_rows(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, ctx.n_requests,
-                                   max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
+                                   max_rows, n_heads, n_kv_heads, head_dim, ctx.page_size, window, scale, **extra)
         if n_small == ctx.n_requests:
             return
     if wide:
         # prompt portions in bfloat16 storage: tensor cores, with float32 scores and the weights in two bfloat16 terms
         work_req, work_pair0, n_work = ctx.attention_work(group, kernels.ATTENTION_WIDE_ROWS, max_rows if n_small else 0)
         kernels.attention_wide(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, work_req, work_pair0,
-                               n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
+                               n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, window, scale, **extra)
         return
     work_req, work_pair0, n_work = ctx.attention_work(group, 32, max_rows if n_small else 0)
     kernels.attention_general(q, out, kpool, vpool, kvctx.block_table, ctx.q_start, ctx.ctx_before, work_req, work_pair0,
-                              n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, None, scale, **extra)
+                              n_work, n_heads, n_kv_heads, head_dim, ctx.page_size, window, scale, **extra)
 
 
 LIBRARY_HEADS_MIN_ROWS = 64   # rows from which a per-head product in bfloat16 goes to the library's batched product
@@ -115,14 +120,22 @@ class LatentAttention:
     @staticmethod
     def expected_tensors(spec):
         qd = spec.head_dim + spec.rot_dim
-        out = {
-            spec.q_proj: ExpectedTensor((spec.n_heads * qd, spec.hidden)),
+        out = {}
+        if spec.q_rank:
+            out[spec.q_down] = ExpectedTensor((spec.q_rank, spec.hidden))
+            out[spec.q_norm] = ExpectedTensor((spec.q_rank,), init="gain")
+        out.update({
+            spec.q_proj: ExpectedTensor((spec.n_heads * qd, spec.q_rank or spec.hidden)),
             spec.down_proj: ExpectedTensor((spec.kv_rank + spec.rot_dim, spec.hidden)),
             spec.latent_norm: ExpectedTensor((spec.kv_rank,), init="gain"),
             spec.k_up: ExpectedTensor((spec.n_heads * spec.head_dim, spec.kv_rank)),
             spec.v_up: ExpectedTensor((spec.n_heads * spec.v_head_dim, spec.kv_rank)),
-        }
+        })
         out.update(position_class(spec.position).expected_tensors(spec.position))
+        if spec.sink is not None:
+            out[spec.sink] = ExpectedTensor((spec.n_heads,))
+        if spec.head_gate is not None:
+            out[spec.head_gate] = ExpectedTensor((spec.n_heads, spec.hidden))
         out[spec.o_proj] = ExpectedTensor((spec.hidden, spec.n_heads * spec.v_head_dim))
         return out
 
@@ -137,11 +150,28 @@ class LatentAttention:
         inv_freq, rot_dims, _, _ = _rotation(self.position)
         if inv_freq is not None and rot_dims != r:
             raise ValueError(f"the rotation turns {rot_dims} dimensions, the rotated part has {r}")
-        ws = [tensors[spec.q_proj], tensors[spec.down_proj]]
-        dtype = _common_dtype(ws)
-        self.proj = Linear(torch.cat([w.to(dtype) for w in ws], dim=0).contiguous(), rt, "latent_proj")
+        if spec.window is not None and (spec.window <= 0 or spec.chunk):
+            raise ValueError("a window must be positive, and a layer has a window or chunks, not both")
+        # one product of the mixer's input: the queries (or, with queries through a compressed vector of their own, that
+        # vector before its norm), the key/value row, and the heads' output gates
+        self.q_rank = int(spec.q_rank or 0)
+        if self.q_rank and r:
+            raise NotImplementedError("queries through a compressed vector together with a rotated part are not built")
+        ws = [tensors[spec.q_down] if self.q_rank else tensors[spec.q_proj], tensors[spec.down_proj]]
+        if spec.head_gate is not None:
+            ws.append(tensors[spec.head_gate])
+        stacked, self.cols = stack_rows(ws, _common_dtype(ws))
+        self.proj = Linear(stacked, rt, "latent_proj")
         self.q_width = H * self.q_dim
+        self.first_width = self.q_rank or self.q_width
+        self.gate_width = H if spec.head_gate is not None else 0
         self.latent_gain = tensors[spec.latent_norm].contiguous()
+        if self.q_rank:
+            self.q_up = Linear(tensors[spec.q_proj], rt, "latent_q_up")
+            self.q_gain = tensors[spec.q_norm].contiguous()
+            if self.q_gain.dtype != self.latent_gain.dtype:
+                self.q_gain, self.latent_gain = self.q_gain.float(), self.latent_gain.float()
+        self.sink = tensors[spec.sink].float().contiguous() if spec.sink is not None else None
         # the query's way into the compressed space, a matrix per head: [[k_up_h, 0], [0, 1]] maps [q_un, q_rot] to
         # [k_up_h^T q_un, q_rot] (the rotated part passes through exactly)
         uk = tensors[spec.k_up]
@@ -156,29 +186,43 @@ class LatentAttention:
     def cache_requirement(self) -> CacheRequirement:
         s = self.spec
         return CacheRequirement(kind="kv", n_kv_heads=1, head_dim=self.row_dim, v_head_dim=s.kv_rank, dtype=self.rt.act_dtype,
-                                values_in_keys=True, chunk=s.chunk)
+                                values_in_keys=True, chunk=s.chunk, window=s.window)
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         s, rt = self.spec, self.rt
         n = x.shape[0]
         H, kr = s.n_heads, s.kv_rank
-        proj = self.proj(x, rt.ws.take("latent_proj", (n, self.q_width + self.row_dim), rt.act_dtype))
-        q, row = proj[:, :self.q_width], proj[:, self.q_width:]
+        cols = self.cols
+        proj = self.proj(x, rt.ws.take("latent_proj", (n, cols[-1]), rt.act_dtype))
+        q, row = proj[:, :self.first_width], proj[:, cols[1]:cols[1] + self.row_dim]
         kvctx = ctx.kv[cache.group]
         inv_freq, rot_dims, neighbours, mult = _rotation(self.position)
-        # norm of the compressed part, rotation of the shared key part and of every head's rotated part, cache write
-        kernels.head_prepare(q, H, self.q_dim, row, 1, self.row_dim, ctx.positions, kvctx.slot_mapping,
-                             cache.k if cache.write else None, ctx.page_size, k_gain=self.latent_gain, k_norm_dims=kr,
-                             eps=s.norm_eps, inv_freq=inv_freq, rot_dims=rot_dims, q_rot_off=s.head_dim, k_rot_off=kr,
-                             neighbours=neighbours, mult=mult)
+        kpool = cache.k if cache.write else None
+        if self.q_rank:
+            # the norms of both compressed vectors and the cache write (the queries' vector is one "head" of q_rank
+            # numbers here), then the queries' expansion
+            kernels.head_prepare(q, 1, self.q_rank, row, 1, self.row_dim, ctx.positions, kvctx.slot_mapping, kpool,
+                                 ctx.page_size, q_gain=self.q_gain, q_norm_dims=self.q_rank, k_gain=self.latent_gain,
+                                 k_norm_dims=kr, eps=s.norm_eps)
+            q = self.q_up(q, rt.ws.take("latent_q", (n, self.q_width), rt.act_dtype))
+        else:
+            # norm of the compressed part, rotation of the shared key part and of every head's rotated part, cache write
+            kernels.head_prepare(q, H, self.q_dim, row, 1, self.row_dim, ctx.positions, kvctx.slot_mapping, kpool,
+                                 ctx.page_size, k_gain=self.latent_gain, k_norm_dims=kr, eps=s.norm_eps,
+                                 inv_freq=inv_freq, rot_dims=rot_dims, q_rot_off=s.head_dim, k_rot_off=kr,
+                                 neighbours=neighbours, mult=mult)
         qc = rt.ws.take("latent_qc", (n, H * self.row_dim), rt.act_dtype)
         heads_product(q, self.q_dim, self.absorb, qc, self.row_dim)
         mixed = rt.ws.take("latent_mixed", (n, H * kr), rt.act_dtype)
         attend_float32(qc, mixed, cache.k, cache.k, ctx, kvctx, H, 1, self.row_dim, kr, float(s.scale), s.chunk,
-                       n_v_heads=1, v_row=self.row_dim)
+                       n_v_heads=1, v_row=self.row_dim, window=s.window, sink=self.sink)
         heads = rt.ws.take("latent_heads", (n, H * s.v_head_dim), rt.act_dtype)
         heads_product(mixed, kr, self.expand, heads, s.v_head_dim)
+        if self.gate_width:
+            # a head's output times sigmoid of its gate
+            kernels.gate_mul(heads, proj[:, cols[2]:cols[2] + H], group=s.v_head_dim)
         return self.o(heads, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
+
 
 
 @register_mixer("differential_attention")

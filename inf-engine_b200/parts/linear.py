@@ -17,6 +17,24 @@ import torch
 from .. import kernels
 
 
+def stack_rows(weights: list[torch.Tensor], dtype: torch.dtype, align: int = 8) -> tuple[torch.Tensor, list[int]]:
+    """Several weights that read the same input, stacked into one ([sum of rows, in]) so that one product serves them
+    all; every part starts at a row that is a multiple of ``align`` (rows of zeros between them), so that the parts of
+    the product's result are column slices that start on 16 bytes.  Returns the stacked weight and the first row of
+    every part, with the total as the last entry (also a multiple of ``align``)."""
+    parts, starts, at = [], [], 0
+    for w in weights:
+        starts.append(at)
+        parts.append(w.to(dtype))
+        at += w.shape[0]
+        pad = -at % align
+        if pad:
+            parts.append(torch.zeros((pad, w.shape[1]), dtype=dtype, device=w.device))
+            at += pad
+    starts.append(at)
+    return torch.cat(parts, dim=0).contiguous(), starts
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor, rt, name: str = "linear", bias: torch.Tensor | None = None):
         """``bias`` ([out_features], optional) is added to the product by ``__call__`` (the fused streaming entries
@@ -65,8 +83,10 @@ class Linear:
         if x.dtype is torch.float32 or w.dtype is torch.float32:
             kernels.gemm_simt(x, w, out)
             return out
-        # bfloat16 x bfloat16
-        if self.streams(x.shape[0]) and out.dtype in (torch.bfloat16, torch.float32):
+        # bfloat16 x bfloat16 (the streaming kernel reads rows in 16-byte pieces: a column slice that starts or strides
+        # off such a boundary goes to the library product)
+        if (self.streams(x.shape[0]) and out.dtype in (torch.bfloat16, torch.float32) and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0):
             return self.stream(x, out, x.shape[0], "bf16" if out.dtype is torch.bfloat16 else "f32")
         if out.dtype is torch.bfloat16 and out.is_contiguous():
             torch.mm(x, w.t(), out=out)

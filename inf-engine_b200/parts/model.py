@@ -54,7 +54,9 @@ class DecoderModel:
             if e.cache_from is not None:
                 reqs.append(CacheRequirement(kind="none"))
             else:
-                reqs.append(self.layers[e.layer].mixer.cache_requirement())
+                # a block that keeps something of its own beside its mixer's cache says so itself
+                blk = self.layers[e.layer]
+                reqs.append(blk.cache_requirement() if hasattr(blk, "cache_requirement") else blk.mixer.cache_requirement())
         return reqs
 
     def bind_cache(self, manager: CacheManager) -> None:
@@ -197,6 +199,51 @@ class ReinjectDecoderModel(DecoderModel):
         if pending is not None:
             kernels.residual_add(residual, pending)
         kernels.residual_add(residual, self._embedded)
+        ctx.handover = None
+        ctx.residual_cast = None
+        return residual, None
+
+
+@register_model("pass_offset_decoder")
+class PassOffsetDecoderModel(DecoderModel):
+    """``DecoderModel`` whose first residual is the token embedding times a constant plus a sinusoidal position vector,
+    and which adds a learned vector to the stream right before the schedule entries that the spec names
+    (``PassOffsetDecoderSpec``): the vector of a pass before the first layer of every pass of a repeated group."""
+
+    @staticmethod
+    def expected_tensors(spec) -> dict:
+        out = DecoderModel.expected_tensors(spec)
+        if spec.pass_offsets is None:
+            return out
+        rows = 1 + max((r for _, r in spec.offset_before), default=0)
+        first = {spec.embedding: out.pop(spec.embedding), spec.pass_offsets: ExpectedTensor((rows, spec.hidden))}
+        first.update(out)
+        return first
+
+    def __init__(self, spec, tensors: dict, rt):
+        super().__init__(spec, tensors, rt)
+        self.offsets = {}
+        for entry, row in spec.offset_before:
+            if not 0 <= entry < len(spec.schedule) or spec.pass_offsets is None:
+                raise ValueError(f"no vector can be added before schedule entry {entry}")
+            self.offsets[int(entry)] = tensors[spec.pass_offsets][int(row)].contiguous()
+
+    def embed(self, ctx) -> torch.Tensor:
+        residual = super().embed(ctx)
+        s = self.spec
+        if s.sinusoid_base > 0:
+            kernels.scale_add_sinusoid(residual, ctx.positions, s.embedding_scale, s.sinusoid_base)
+        elif s.embedding_scale != 1.0:
+            kernels.scale_rows(residual, s.embedding_scale)
+        return residual
+
+    def before_entry(self, i: int, residual, pending, ctx):
+        row = self.offsets.get(i)
+        if row is None:
+            return residual, pending
+        if pending is not None:
+            kernels.residual_add(residual, pending)
+        kernels.add_row(residual, row)
         ctx.handover = None
         ctx.residual_cast = None
         return residual, None

@@ -1,4 +1,5 @@
-"""A mixture of gated feed-forward experts with a sigmoid router, chosen and run on the device.
+"""A mixture of gated feed-forward experts, chosen and run on the device: a sigmoid router with groups, or (``score``
+"softmax_top") the largest logits plus a bias, weighted by the softmax over the chosen logits alone.
 
 Per token, with x the part's input (``RoutedExpertsSpec`` states the rule in full):
 
@@ -40,6 +41,8 @@ class RoutedExperts:
         out[spec.router] = ExpectedTensor((spec.n_experts, spec.hidden))
         if spec.correction is not None:
             out[spec.correction] = ExpectedTensor((spec.n_experts,))
+        if spec.router_bias is not None:
+            out[spec.router_bias] = ExpectedTensor((spec.n_experts,))
         if spec.shared is not None:
             out.update(GatedMLP.expected_tensors(spec.shared))
             out[spec.shared_gate] = ExpectedTensor((1, spec.hidden))
@@ -51,6 +54,12 @@ class RoutedExperts:
             raise ValueError(f"{E} experts in {spec.n_groups} groups of which {spec.keep_groups} are kept: not possible")
         if not 0 < spec.top <= spec.keep_groups * (E // spec.n_groups):
             raise ValueError(f"{spec.top} experts cannot be chosen from {spec.keep_groups} groups of {E // spec.n_groups}")
+        if spec.score not in kernels.ROUTE_SCORES:
+            raise ValueError(f"router score {spec.score!r} is not built (known: {', '.join(kernels.ROUTE_SCORES)})")
+        if spec.score == "softmax_top" and (spec.n_groups != 1 or spec.correction is not None):
+            raise ValueError("a router whose weights are the softmax over the chosen logits has no groups and no correction")
+        if spec.score != "softmax_top" and spec.router_bias is not None:
+            raise ValueError("a bias of the router's logits belongs to the softmax over the chosen logits")
         self.spec = spec
         self.rt = rt
         names = [f"{spec.expert_prefix}{e}." for e in range(E)]
@@ -65,6 +74,8 @@ class RoutedExperts:
         rdtype = torch.float32 if any(t.dtype is torch.float32 for t in rows) else rows[0].dtype
         self.router = torch.cat([t.to(rdtype) for t in rows], dim=0).contiguous()
         self.correction = tensors[spec.correction].contiguous() if spec.correction is not None else None
+        if spec.router_bias is not None:
+            self.correction = tensors[spec.router_bias].contiguous()      # the route kernel adds it to the logits
         self.shared = GatedMLP(spec.shared, tensors, rt) if spec.shared is not None else None
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
@@ -78,7 +89,7 @@ class RoutedExperts:
         weights = ws.take("moe_weights", (n, top), torch.float32)
         gate = ws.take("moe_gate", (n,), torch.float32) if self.shared is not None else None
         kernels.moe_route(logits, self.correction, ids, weights, gate, E, top, s.n_groups, s.keep_groups, s.route_scale,
-                          s.weight_eps, gate_col=E if self.shared is not None else -1)
+                          s.weight_eps, gate_col=E if self.shared is not None else -1, score=s.score)
         sorted_pairs = ws.take("moe_sorted", (n_pairs,), torch.int32)
         tiles = ws.take("moe_tiles", (kernels.moe_max_tiles(n_pairs, E), 4), torch.int32)
         kernels.moe_sort(ids, E, sorted_pairs, tiles)
