@@ -140,10 +140,16 @@ def mlstm(h, m: dict, w: dict, p: str, eps: float, round_to=None, gates_round_to
     return lin(w[p + "o"], rnd(o, round_to), round_to)
 
 
-def route(h, r: dict, w: dict, p: str):
-    """(chosen experts [T, top], their weights [T, top]): the largest logits, softmax over those alone."""
+def route(h, r: dict, w: dict, p: str, gaps: list | None = None):
+    """(chosen experts [T, top], their weights [T, top]): the largest logits, softmax over those alone.  ``gaps`` takes,
+    per token, how far the last chosen logit lies above the best one left out, in units of the logits' spread (a small
+    gap is a close call that rounding may decide either way)."""
     z = lin(w[p + "router"], h, None, w[p + "router.b"])
-    top = torch.topk(z, int(r["top"]), dim=-1)
+    k = int(r["top"])
+    top = torch.topk(z, k, dim=-1)
+    if gaps is not None and k < z.shape[-1]:
+        both = torch.topk(z, k + 1, dim=-1).values
+        gaps.append((both[:, k - 1] - both[:, k]) / z.std().clamp_min(1e-12))
     return top.indices, torch.softmax(top.values, dim=-1)
 
 
@@ -153,8 +159,8 @@ def expert(x, w: dict, p: str, round_to=None):
     return lin(w[p + "down"], rnd(g * torch.sigmoid(g) * u, round_to), None)
 
 
-def mixture(h, mlp: dict, w: dict, p: str, round_to=None):
-    ids, wts = route(h, mlp["router"], w, p)
+def mixture(h, mlp: dict, w: dict, p: str, round_to=None, gaps: list | None = None):
+    ids, wts = route(h, mlp["router"], w, p, gaps)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(ids[t].tolist(), wts[t]):
@@ -178,8 +184,10 @@ def run_order(cfg: dict) -> list[tuple[int, int | None]]:
     return order + [(i, None) for i in range(b, n)]
 
 
-def forward(cfg: dict, w: dict, tokens: list[int], round_to=None, collect: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of a whole sequence; ``collect`` takes the residual stream after every run of a layer."""
+def forward(cfg: dict, w: dict, tokens: list[int], round_to=None, collect: list | None = None,
+            gaps: list | None = None) -> torch.Tensor:
+    """Logits [T, vocab] of a whole sequence; ``collect`` takes the residual stream after every run of a layer, ``gaps``
+    the routers' margins of every run of a mixture (see ``route``)."""
     eps = float(cfg["norm"]["eps"])
     width = int(cfg["width"])
     T = len(tokens)
@@ -196,7 +204,17 @@ def forward(cfg: dict, w: dict, tokens: list[int], round_to=None, collect: list 
         x = x + offset_norm(MIXERS[L["type"]](h, L["mixer"], w, p + "mix.", eps, round_to), w[p + "norm1b"], eps)
         if L.get("mlp") is not None:
             h = rnd(offset_norm(x, w[p + "norm2"], eps), round_to)
-            x = x + offset_norm(mixture(h, L["mlp"], w, p + "mlp.", round_to), w[p + "norm2b"], eps)
+            x = x + offset_norm(mixture(h, L["mlp"], w, p + "mlp.", round_to, gaps), w[p + "norm2b"], eps)
         if collect is not None:
             collect.append(x.clone())
     return lin(w["head"], rnd(offset_norm(x, w["final.norm"], eps), round_to), None)
+
+
+def forward_float32(cfg: dict, w: dict, tokens: list[int]) -> torch.Tensor:
+    """The same model with every number a 32-bit float (how far 32-bit arithmetic alone moves the logits)."""
+    global F
+    F = torch.float32
+    try:
+        return forward(cfg, w, tokens).double()
+    finally:
+        F = torch.float64
