@@ -441,6 +441,30 @@ def _fovunex_configs(size):
 FOVUNEX_CHUNK, FOVUNEX_RANK, FOVUNEX_ROT = 1024, 192, 64
 
 
+def _gavatar_configs(size):
+    """A Gavatar model of the size's width (a matrix memory, attention with weights mixed across heads under a window of
+    1,024 keys, a matrix memory, latent attention over compressed rows of 192 numbers with a sink under the same window;
+    every layer with 16 experts of which a token runs four: as many ACTIVE feed-forward parameters as the dense models)
+    and the Kipezen model of equal width, depth and head geometry, the closest family the engine had (a routed mixture of
+    experts, windowed attention, a gated recurrence with a float32 matrix state per head)."""
+    from inf_engine_b200.config import parse_config_dict
+    z = FAMILY_SIZES[size]
+    w, H, G, inter = z["width"], z["heads"], z["kv"], z["inter"]
+    mlp = {"kind": "moe", "expert": {"ff": inter // 4}, "router": {"experts": 16, "top": 4}}
+    mem = {"type": "mlstm", "mixer": {"heads": H, "dim": FAMILY_HD, "vdim": FAMILY_HD, "gate_cap": 15.0}, "mlp": mlp}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": H, "kv_heads": G, "dim": FAMILY_HD, "vdim": FAMILY_HD, "scale": 8.0, "mask": {"size": GAVATAR_WINDOW}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": H, "dim": FAMILY_HD, "vdim": FAMILY_HD, "q_rank": w // 2, "kv_rank": GAVATAR_RANK,
+                     "scale": FAMILY_HD ** -0.5, "mask": {"size": GAVATAR_WINDOW}}}
+    gav = parse_config_dict({"architecture": "Gavatar", "vocab": FAMILY_VOCAB, "width": w, "norm": {"eps": 1e-5},
+                             "embedding": {"scale": float(w) ** 0.5}, "layers": [mem, att, mem, lat]})
+    return gav, _kipezen_configs(size)[0]
+
+
+GAVATAR_WINDOW, GAVATAR_RANK = 1024, 192
+
+
 def _weight_bytes(runner):
     seen, n = set(), 0
     import torch
@@ -466,8 +490,8 @@ def run_family(args):
     from inf_engine_b200 import Engine, StepEntry, SamplingConfig, kernels
     from inf_engine_b200.sampling import pack_rows, request_key
 
-    if args.family not in ("barerax", "kipezen", "fovunex"):
-        print(f"--family {args.family}: unknown (known: barerax, kipezen, fovunex)")
+    if args.family not in ("barerax", "kipezen", "fovunex", "gavatar"):
+        print(f"--family {args.family}: unknown (known: barerax, kipezen, fovunex, gavatar)")
         return 2
     pk = peaks()
     torch.cuda.set_device(0)
@@ -1013,8 +1037,188 @@ def run_family(args):
             timed(lambda: lat_att(ctx_d, B)), like_decode, B * N * rd * 2, like_decode_bytes)
         return rows
 
+    def gavatar_kernel_table(size):
+        """Every kernel that the Gavatar family added, alone, beside the like kernel of the closest family (Kipezen), at
+        2,048 tokens of one request and at 8 requests of one token over 2,048 keys."""
+        from inf_engine_b200.engine.batch import KVGroupContext, StepContext
+        from inf_engine_b200.parts import CacheView, Runtime
+        from inf_engine_b200.parts.attention import PagedAttention
+        from inf_engine_b200.parts.latent import attend_float32, heads_product
+        z = FAMILY_SIZES[size]
+        W, H, G, hd, inter = z["width"], z["heads"], z["kv"], FAMILY_HD, z["inter"]
+        N, B, dev, bf = PROMPT_LEN, 8, "cuda", torch.bfloat16
+        g = torch.Generator(device=dev).manual_seed(1)
+        rnd = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.5)
+        i32 = lambda v: torch.as_tensor(v, dtype=torch.int32, device=dev)
+        rows = []
+
+        def add(name, like, ms, ms_like, nbytes=None, nbytes_like=None, flops=None, flops_like=None, note=None):
+            rec = {"kernel": name, "like": like, "ms": ms, "like_ms": ms_like}
+            if nbytes is not None:
+                rec["frac_of_hbm"] = nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+                if ms_like:
+                    rec["like_frac_of_hbm"] = (nbytes_like or nbytes) / (ms_like * 1e-3) / 1e9 / pk["hbm_gbs"]
+            if flops is not None:
+                rec["frac_of_bf16"] = flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+                if ms_like:
+                    rec["like_frac_of_bf16"] = (flops_like or flops) / (ms_like * 1e-3) / 1e12 / pk["bf16_tflops"]
+            if note:
+                rec["note"] = note
+            rows.append(rec)
+
+        rt = Runtime(dev, bf)
+        n_pages = B * N // PAGE
+        qs1, sl1 = i32([0, N]), i32([0])
+        qs8, sl8 = torch.arange(B + 1, dtype=torch.int32, device=dev), torch.arange(B, dtype=torch.int32, device=dev)
+
+        def context(q_lens, before):
+            ctx = StepContext(rt, PAGE)
+            R, n = len(q_lens), sum(q_lens)
+            ctx.n_tokens, ctx.n_requests, ctx.n_logits = n, R, 0
+            starts = [0]
+            for ql in q_lens:
+                starts.append(starts[-1] + ql)
+            per = n_pages // R
+            ctx.q_start, ctx.ctx_before = i32(starts), i32(before)
+            ctx.positions = i32([b + t for ql, b in zip(q_lens, before) for t in range(ql)])
+            ctx.slots = i32(list(range(R)))
+            table_ = torch.arange(per * R, dtype=torch.int32, device=dev).view(R, per)
+            sm = i32([(r * per + (b + t) // PAGE) * PAGE + (b + t) % PAGE for r, (ql, b) in enumerate(zip(q_lens, before)) for t in range(ql)])
+            ctx.kv = [KVGroupContext(sm, table_)]
+            ctx.host = {"q_lens": list(q_lens), "ctx_before": list(before), "q_start": starts}
+            ctx.max_q_len, ctx.max_seq_len = max(q_lens), max(b + ql for ql, b in zip(q_lens, before))
+            ctx.keys_cap = ctx.max_seq_len
+            return ctx
+
+        ctx_p, ctx_d = context([N], [0]), context([1] * B, [N - 1] * B)
+        window = GAVATAR_WINDOW
+        pairs_all = N * (N + 1) // 2
+        pairs_w = pairs_all - (N - window) * (N - window + 1) // 2
+        # elementwise passes of the stream | the like passes of the closest families
+        res, y = rnd(N, W), rnd(N, W).to(bf)
+        nxt, gain = torch.empty(N, W, device=dev, dtype=bf), (1 + 0.1 * rnd(W))
+        silu_in, silu_out = rnd(N, 2 * W).to(bf), torch.empty(N, W, device=dev, dtype=bf)
+        like_silu = timed(lambda: kernels.silu_mul(silu_in, silu_out, interleaved=True))
+        add("scaled embedding + sinusoidal position vector", "scale of the embedding (Fovunex)",
+            timed(lambda: kernels.scale_add_sinusoid(res, ctx_p.positions, 1.0, 10000.0)), timed(lambda: kernels.scale_rows(res, 1.0)),
+            N * W * 8, N * W * 8)
+        h_in, h_out, mu, last = rnd(N, W).to(bf), torch.empty(N, W, device=dev, dtype=bf), rnd(W).to(bf), torch.zeros(16, W, device=dev, dtype=bf)
+        add("token shift of the mixer's input, prompt", "silu_mul over rows of the same width",
+            timed(lambda: kernels.token_shift(h_in, h_out, mu, last, qs1, i32([0]), sl1, 1)), like_silu, N * W * 6, N * W * 6)
+        add("token shift of the mixer's input, decode b8", "silu_mul, 8 rows",
+            timed(lambda: kernels.token_shift(h_in[:B], h_out[:B], mu, last, qs8, i32([N - 1] * B), sl8, B)),
+            timed(lambda: kernels.silu_mul(silu_in[:B], silu_out[:B], interleaved=True)), B * W * 8, B * W * 6)
+        add("norm of a sublayer's output into the residual (the block's second norm)", "the same kernel in Kipezen",
+            timed(lambda: kernels.outnorm_accumulate(res, y, gain, 1e-5, None)), timed(lambda: kernels.outnorm_accumulate(res, y, gain, 1e-5, nxt)),
+            N * W * (4 + 4 + 2), N * W * (4 + 4 + 2 + 2))
+        # attention with mixed heads: biases, head norms of q, k and v, cache write | Kipezen's prepare kernel
+        qkv = rnd(N, (H + 2 * G) * hd).to(bf)
+        q, kx, v = qkv[:, :H * hd], qkv[:, H * hd:(H + G) * hd], qkv[:, (H + G) * hd:]
+        kpool = torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf)
+        vpool = torch.zeros(n_pages, 1, PAGE, G * hd, device=dev, dtype=bf)
+        vpool_k = torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf)
+        qb, kb, vb = rnd(H * hd).to(bf), rnd(G * hd).to(bf), rnd(G * hd).to(bf)
+        qg, kg = (1 + 0.1 * rnd(H * hd)).to(bf), (1 + 0.1 * rnd(G * hd)).to(bf)
+        inv_freq = (10000.0 ** (-2.0 * torch.arange(hd // 4, dtype=torch.float64) / (hd // 2))).to(dev)
+        like_prepare = timed(lambda: kernels.rownorm_rotate_write(q, kx, v, qb, kb, vb, qg, kg, 1e-5, inv_freq, hd // 2, ctx_p.positions,
+                                                                  ctx_p.kv[0].slot_mapping, kpool, vpool_k, H, G, hd, hd, PAGE))
+        add("biases + head norms of q, k and v + cache write", "biases + whole-row norm + pair rotation + cache write",
+            timed(lambda: kernels.qkv_prepare(q, H, kx, G, hd, v, G, hd, ctx_p.kv[0].slot_mapping, kpool, vpool, PAGE, 1e-5, q_bias=qb,
+                                              k_bias=kb, v_bias=vb, q_norm=True, k_norm=True, v_norm=True, pool_v_heads=1)),
+            like_prepare, N * (H + 2 * G) * hd * 2 * 2, N * (H + 2 * G) * hd * 2 * 2)
+        kpz = _kipezen_configs(size)[0]
+        spec_k = kpz.model_spec().layers[3].mixer.branches[0]
+        tensors = {n: ((1 + 0.1 * rnd(*e.shape)) if e.init == "gain" else rnd(*e.shape) * 0.1).to(bf)
+                   for n, e in PagedAttention.expected_tensors(spec_k).items()}
+        att_k = PagedAttention(spec_k, tensors, rt)
+        view_k = CacheView("kv", 0, kpool, vpool_k, None, True)
+        out_k = torch.empty(N, H * hd, device=dev, dtype=bf)
+        like_att = lambda ctx, n: att_k._attend(q[:n], out_k[:n], view_k, ctx, ctx.kv[0], head_scale=att_k.head_scale)
+        pairs_k = pairs_w + 4 * (N - window - 4)
+        like_prompt, like_decode = timed(lambda: like_att(ctx_p, N), reps=5), timed(lambda: like_att(ctx_d, B))
+        like_prompt_flops, like_decode_bytes = 4 * H * hd * pairs_k, B * (window + 4) * G * hd * 2 * 2
+        slice_heads = max(1, min(G, 256 // hd))
+        values = vpool.view(n_pages, PAGE, G * hd)
+        talk, gate_ = rnd(H, H), rnd(N, H * hd).to(bf)
+        unmixed, tout = torch.empty(N, H * slice_heads * hd, device=dev, dtype=bf), torch.empty(N, H * hd, device=dev, dtype=bf)
+
+        def talking(ctx, n, combine=True):
+            for c0 in range(0, G, slice_heads):
+                nc = min(slice_heads, G - c0)
+                attend_float32(q[:n], unmixed[:n, :H * nc * hd], kpool, values[:, :, c0 * hd:], ctx, ctx.kv[0], H, G, hd, nc * hd, 0.125,
+                               None, n_v_heads=1, v_row=G * hd, window=window)
+                if combine:
+                    kernels.talk_combine(unmixed[:n, :H * nc * hd], talk, gate_[:n], tout[:n], H, G, hd, first_v_head=c0, slice_v_heads=nc)
+        # what the mechanism asks for: scores and weights of every head at every pair, the H x H mix, one value head a head
+        useful = 2 * H * (2 * hd + H) * pairs_w
+        add("attention with weights mixed across heads, prompt (window 1,024; every head over all value heads, then the mix)",
+            "attention, prompt (window of 1,024 + 4 kept keys)", timed(lambda: talking(ctx_p, N), reps=5), like_prompt,
+            flops=useful, flops_like=like_prompt_flops,
+            note="useful FLOPs (scores, the mix, one value head a head); the launches do %.1f times that: every head meets all %d value heads"
+                 % (2 * H * (-(-G // slice_heads) * hd + G * hd) * pairs_w / useful, G))
+        add("attention with weights mixed across heads, decode b8 x 2,048 keys (1,024 visible)", "attention, decode (1,028 visible)",
+            timed(lambda: talking(ctx_d, B)), like_decode, B * window * 2 * G * hd * 2, like_decode_bytes)
+        add("mix of the heads' results + output gate (one launch a slice of value heads)", "silu_mul",
+            timed(lambda: kernels.talk_combine(unmixed, talk, gate_, tout, H, G, hd, first_v_head=0, slice_v_heads=slice_heads)), like_silu,
+            N * (H * slice_heads * hd + 2 * H * hd // (G // slice_heads)) * 2, N * W * 6)
+        # latent attention with a sink under a window | Kipezen's windowed attention
+        kr = GAVATAR_RANK
+        cq, row = rnd(N, W // 2).to(bf), rnd(N, kr).to(bf)
+        lpool = torch.zeros(n_pages, 1, PAGE, kr, device=dev, dtype=bf)
+        cg, lg = (1 + 0.1 * rnd(W // 2)).to(bf), (1 + 0.1 * rnd(kr)).to(bf)
+        add("norms of both compressed vectors + cache write (latent)", "biases + whole-row norm + pair rotation + cache write",
+            timed(lambda: kernels.head_prepare(cq, 1, W // 2, row, 1, kr, ctx_p.positions, ctx_p.kv[0].slot_mapping, lpool, PAGE, q_gain=cg,
+                                               q_norm_dims=W // 2, k_gain=lg, k_norm_dims=kr, eps=1e-5)),
+            like_prepare, N * (W // 2 * 2 + kr * 2) * 2, N * (H + 2 * G) * hd * 2 * 2)
+        ql, qc = rnd(N, H * hd).to(bf), torch.empty(N, H * kr, device=dev, dtype=bf)
+        mixed, heads = torch.empty(N, H * kr, device=dev, dtype=bf), torch.empty(N, H * hd, device=dev, dtype=bf)
+        sink = rnd(H)
+        lat_att = lambda ctx, n: attend_float32(qc[:n], mixed[:n], lpool, lpool, ctx, ctx.kv[0], H, 1, kr, kr, hd ** -0.5, None,
+                                                n_v_heads=1, v_row=kr, window=window, sink=sink)
+        add("attention, prompt (latent: %d heads over one row of %d, window 1,024, a sink)" % (H, kr),
+            "attention, prompt (window of 1,024 + 4 kept keys)", timed(lambda: lat_att(ctx_p, N), reps=5), like_prompt,
+            flops=2 * H * 2 * kr * pairs_w, flops_like=like_prompt_flops)
+        add("attention, decode b8 x 2,048 keys (latent, 1,024 visible)", "attention, decode (1,028 visible)",
+            timed(lambda: lat_att(ctx_d, B)), like_decode, B * window * kr * 2, like_decode_bytes)
+        hgate = rnd(N, H).to(bf)
+        add("a head's output times sigmoid of its gate", "silu_mul", timed(lambda: kernels.gate_mul(heads, hgate, group=hd)), like_silu,
+            N * H * hd * 4, N * W * 6)
+        # the matrix memory | the gated delta rule of Kipezen (the same head geometry: a float32 matrix of 64 x 64 a head)
+        Wd = H * hd
+        proj = rnd(N, 4 * Wd).to(bf)
+        mq, mk, mv, mg = (proj[:, i * Wd:(i + 1) * Wd] for i in range(4))
+        zg, ib, fb = rnd(N, 2 * H) * 3, rnd(H).to(bf), (3 + rnd(H)).to(bf)
+        words = kernels.mlstm_state_floats(hd, hd)
+        mst, mo = torch.zeros(16, H, words, device=dev), torch.empty(N, Wd, device=dev)
+        run_mm = lambda n, qs, sl, R: kernels.mlstm_scan(mq[:n], mk[:n], mv[:n], zg[:n], ib, fb, 15.0, mst, mo[:n], qs, sl, R, H, hd, hd)
+        b_pre, a_pre = rnd(N, H).to(bf), rnd(N, H).to(bf)
+        a_log, dt_b, og = rnd(H).to(bf), rnd(H).to(bf), (1 + 0.1 * rnd(hd)).to(bf)
+        gst, gmixed = torch.zeros(16, H, hd, hd, device=dev), torch.empty(N, Wd, device=dev, dtype=bf)
+        run_gd = lambda n, qs, sl, R: kernels.gated_delta(mq[:n, :G * hd], mk[:n, :G * hd], mv[:n], b_pre[:n], a_pre[:n], mg[:n], a_log, dt_b,
+                                                          og, gst, gmixed[:n], qs, sl, R, H, G, hd, hd, 1e-6, 1e-5)
+        add("matrix memory, prompt of 2,048 tokens (one request)", "gated delta rule, prompt",
+            timed(lambda: run_mm(N, qs1, sl1, 1), reps=5), timed(lambda: run_gd(N, qs1, sl1, 1), reps=5),
+            N * (3 * Wd * 2 + Wd * 4) + 2 * H * words * 4, N * (2 * G * hd + 3 * Wd) * 2 + 2 * H * hd * hd * 4,
+            note="a token-by-token scan: the chain of %d dependent steps bounds it, not bytes" % N)
+        add("matrix memory, decode b8", "gated delta rule, decode", timed(lambda: run_mm(B, qs8, sl8, B)), timed(lambda: run_gd(B, qs8, sl8, B)),
+            B * 2 * H * words * 4, B * 2 * H * hd * hd * 4)
+        ogain = (1 + 0.1 * rnd(Wd)).to(bf)
+        add("matrix memory: head norm, gain and output gate", "silu_mul", timed(lambda: kernels.mlstm_finish(mo, ogain, mg, gmixed, H, hd, 1e-5)),
+            like_silu, N * Wd * (4 + 2 + 2), N * W * 6)
+        # the router of the largest logits | Kipezen's router (sigmoid scores in groups)
+        E = 16
+        logits = rnd(N, E + 1) * 2
+        rb = rnd(E)
+        ids4, wts4 = torch.empty(N, 4, dtype=torch.int32, device=dev), torch.empty(N, 4, device=dev)
+        ids2, wts2, gt = torch.empty(N, 2, dtype=torch.int32, device=dev), torch.empty(N, 2, device=dev), torch.empty(N, device=dev)
+        add("router: 4 largest of 16 logits, softmax over the chosen", "router: sigmoid scores, 2 of 16 from 2 of 4 groups",
+            timed(lambda: kernels.moe_route(logits[:, :E], rb, ids4, wts4, None, E, 4, 1, 1, 1.0, 0.0, score="softmax_top")),
+            timed(lambda: kernels.moe_route(logits, None, ids2, wts2, gt, E, 2, 4, 2, 2.5, 1e-20, gate_col=E)),
+            N * (E * 4 + 4 * 8), N * (E * 4 + 2 * 8 + 4))
+        return rows
+
     sizes = {}
-    if args.family in ("kipezen", "fovunex") and args.family_step:
+    if args.family in ("kipezen", "fovunex", "gavatar") and args.family_step:
         # one step launched kernel by kernel (no graphs) between cudaProfilerStart / Stop, for a launch list:
         #   ncu --metrics gpu__time_duration.sum --clock-control none --profile-from-start off --csv --log-file L \
         #       python bench.py --family kipezen --family-sizes w2048 --family-step decode
@@ -1022,7 +1226,7 @@ def run_family(args):
         from inf_engine_b200 import ModelRunner
         from inf_engine_b200.weights import write_random_model
         size = (args.family_sizes or "w2048").split(",")[0]
-        kpz, _ = (_kipezen_configs if args.family == "kipezen" else _fovunex_configs)(size)
+        kpz, _ = {"kipezen": _kipezen_configs, "fovunex": _fovunex_configs, "gavatar": _gavatar_configs}[args.family](size)
         with tempfile.TemporaryDirectory() as tmp:
             write_random_model(kpz, args.seed, tmp)
             r = ModelRunner.from_dir(tmp, dtype="bfloat16", page_size=PAGE, n_pages=(args.batch + 1) * POOL_CONTEXT // PAGE,
@@ -1049,6 +1253,24 @@ def run_family(args):
         torch.cuda.cudart().cudaProfilerStop()
         clocks.stop()
         print(json.dumps({"impl": "ours", "family": args.family, "step": args.family_step, "size": size, "launches": kernels.LAUNCHES}))
+        return 0
+    if args.family == "gavatar":
+        for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
+            gav, kpz = _gavatar_configs(size)
+            rec = {"gavatar": model_numbers_of(gav, args.batch), "kipezen": model_numbers_of(kpz, args.batch)}
+            rec["kernels"] = gavatar_kernel_table(size)
+            sizes[size] = rec
+        clocks.stop()
+        print(json.dumps({"impl": "ours", "family": "gavatar", "dtype": "bf16", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3),
+                          "data": "synthetic: seeded random weights, uniform random prompt ids",
+                          "config": {"layers": FAMILY_LAYERS, "pattern": "matrix memory, attention with mixed heads, matrix memory, latent attention",
+                                     "vocab": FAMILY_VOCAB, "head_dim": FAMILY_HD, "prompt": PROMPT_LEN, "decode_batch": args.batch,
+                                     "page_size": PAGE, "window": GAVATAR_WINDOW, "kv_rank": GAVATAR_RANK,
+                                     "experts": "16, 4 a token",
+                                     "l2": "a 256 MB buffer is written before every timed kernel; model steps stream their weights",
+                                     "sizes": FAMILY_SIZES},
+                          "peaks": pk, "sizes": sizes, "clocks": clocks.summary(t_all0, time.perf_counter())}))
         return 0
     if args.family == "fovunex":
         for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
@@ -1285,11 +1507,11 @@ def main():
     ap.add_argument("--no-workloads", action="store_true",
                     help="leave out the two continuous-batching workloads at the other models' sizes")
     ap.add_argument("--family", default=None, metavar="NAME",
-                    help="instead of the default workload: prefill and decode of another model family (barerax, kipezen, fovunex) at sizes like "
+                    help="instead of the default workload: prefill and decode of another model family (barerax, kipezen, fovunex, gavatar) at sizes like "
                          "a real model's layers, beside the closest earlier model of equal size, and its kernels beside the like ones")
     ap.add_argument("--family-sizes", default=None, help="comma-separated subset of the family's sizes (w1024,w2048)")
     ap.add_argument("--family-step", default=None, choices=["decode", "prefill"],
-                    help="with --family kipezen or fovunex: run one such step kernel by kernel between cudaProfilerStart/Stop (for a launch list) and exit")
+                    help="with --family kipezen, fovunex or gavatar: run one such step kernel by kernel between cudaProfilerStart/Stop (for a launch list) and exit")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
                     help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()

@@ -139,6 +139,57 @@ __global__ void talk_combine_kernel(const TA* __restrict__ a, int a_stride, cons
   }
 }
 
+// bfloat16 rows in 16-byte pieces: a thread forms eight neighbouring coordinates of one head's output
+__global__ void talk_combine_vec_kernel(const bf16* __restrict__ a, int a_stride, const float* __restrict__ talk,
+                                        const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
+                                        int out_stride, int heads, int v_heads, int hd_v, int c0, int nc) {
+  extern __shared__ float ts[];
+  pdl_trigger();
+  for (int i = threadIdx.x; i < heads * heads; i += blockDim.x) ts[i] = talk[i];
+  pdl_wait();
+  __syncthreads();
+  const int n = blockIdx.x;
+  const int rep = heads / v_heads, slice_w = nc * hd_v, per_head = hd_v >> 3;
+  const bf16* an = a + (size_t)n * a_stride;
+  for (int i = threadIdx.x; i < nc * rep * per_head; i += blockDim.x) {
+    const int cl = i / (rep * per_head), rem = i - cl * rep * per_head;
+    const int h = (c0 + cl) * rep + rem / per_head, d = (rem % per_head) << 3;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const float* trow = ts + h * heads;
+    const bf16* src = an + cl * hd_v + d;
+#pragma unroll 4
+    for (int g = 0; g < heads; ++g) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)g * slice_w);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float w = trow[g];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p2[j]);
+        acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+      }
+    }
+    const int col = h * hd_v + d;
+    if (gate != nullptr) {
+      const uint4 gr = *reinterpret_cast<const uint4*>(gate + (size_t)n * gate_stride + col);
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gr);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(gp[j]);
+        acc[2 * j] = acc[2 * j] / (1.f + expf(-f.x));
+        acc[2 * j + 1] = acc[2 * j + 1] / (1.f + expf(-f.y));
+      }
+    }
+    uint4 res;
+    __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) rp[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)n * out_stride + col) = res;
+  }
+}
+
 extern "C" int ie_talk_combine(const void* a, int a_stride, const float* talk, const void* gate, int gate_stride,
                                void* out, int out_stride, int n, int heads, int v_heads, int hd_v, int c0, int nc,
                                int act_dtype, cudaStream_t stream) {
@@ -147,6 +198,14 @@ extern "C" int ie_talk_combine(const void* a, int a_stride, const float* talk, c
     return IE_BAD_SIZE;
   const size_t smem = sizeof(float) * (size_t)heads * heads;
   if (smem > 48 * 1024) return IE_BAD_SIZE;
+  if (act_dtype == IE_BF16 && (hd_v & 7) == 0 && (a_stride & 7) == 0 && (out_stride & 7) == 0 &&
+      ((((uintptr_t)a) | ((uintptr_t)out)) & 15) == 0 &&
+      (gate == nullptr || ((gate_stride & 7) == 0 && (((uintptr_t)gate) & 15) == 0))) {
+    const int work = nc * (heads / v_heads) * (hd_v >> 3);
+    const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
+    return launch_k(talk_combine_vec_kernel, n, threads, smem, stream, (const bf16*)a, a_stride, talk, (const bf16*)gate,
+                    gate_stride, (bf16*)out, out_stride, heads, v_heads, hd_v, c0, nc);
+  }
   if (act_dtype == IE_F32)
     return launch_k(talk_combine_kernel<float>, n, 256, smem, stream, (const float*)a, a_stride, talk,
                     (const float*)gate, gate_stride, (float*)out, out_stride, heads, v_heads, hd_v, c0, nc);

@@ -12,12 +12,16 @@
 // state that the step before left, so a whole prompt, a portion and a single decoded token take the same path and a
 // cut changes nothing.
 //
-// Work split: a block takes one (request, head) and a chunk of CV value columns; a thread holds, for one column, the
-// rows p, p + P, p + 2 P, ... of S (at most MM_ROWS of them) and the same rows of n; the P threads of a column sit side
-// by side in a warp and add their partial sums by shuffles.  Every chunk keeps its own copy of n and m in the state
-// (they are the same numbers; a chunk that finishes early must not overwrite what another has yet to read):
-//     state of a head = S [dk * dv], then for each chunk: n [dk], m.
-// Tokens are staged MM_TILE at a time in shared memory.
+// Work split: a block takes one (request, head) and a chunk of value columns.  A column of S is held by P threads that
+// sit side by side in a warp, each with RP = dk / P consecutive rows (P a power of two, at most MM_ROWS rows a thread);
+// they add their partial sums of S^T q by shuffles.  The normaliser n obeys the very recurrence of a column of S whose
+// value is always one, so the last group of P lanes of EVERY warp holds n as such a column: its sum is n . q, which
+// the warp's value columns take from it by one more shuffle, and nothing crosses warps inside a tile.  Every chunk keeps
+// its own copy of n and m in the state (they are the same numbers; a chunk that finishes early must not overwrite what
+// another has yet to read):  state of a head = S [dk * dv], then for each chunk: n [dk], m.
+// Tokens are staged a tile (up to MM_TILE) at a time in shared memory; the tile after is fetched into registers while a
+// tile runs, so that no load stands in the chain of dependent steps.  Within a tile the maxima are formed one after the
+// other by one thread (an addition and a comparison a token), the three exponentials of every token side by side.
 //
 // mlstm_finish: each head's o is divided by its root mean square over dv (eps inside the root), multiplied by a gain of
 // all heads' size and by sigmoid(gate): float32, written in the activation type.
@@ -25,22 +29,31 @@
 
 #define MM_ROWS 16
 #define MM_TILE 16
-#define MM_THREADS 256
+#define MM_MAX_WARPS 16
+#define MM_FETCH 12     // elements of a tile that a thread fetches ahead into registers, each of q, k and v
 
-static inline int mm_parts(int dk) {
+struct MMGeometry {
+  int P, RP, cols_per_warp, chunks, chunk_cols, warps;
+};
+
+static inline bool mm_geometry(int dk, int dv, MMGeometry& g) {
+  if (dk <= 0 || dv <= 0) return false;
   int p = 1;
   while (p * MM_ROWS < dk) p <<= 1;
-  return p;
-}
-static inline int mm_chunk_cols(int dk, int dv) {
-  const int cv = MM_THREADS / mm_parts(dk);
-  return dv < cv ? dv : cv;
+  if (p > 16) return false;                              // a warp needs a group of lanes for n beside a value column
+  g.P = p;
+  g.RP = (dk + p - 1) / p;
+  g.cols_per_warp = 32 / p - 1;
+  const int most = MM_MAX_WARPS * g.cols_per_warp;       // value columns of a block at most
+  g.chunks = (dv + most - 1) / most;
+  g.chunk_cols = (dv + g.chunks - 1) / g.chunks;
+  g.warps = (g.chunk_cols + g.cols_per_warp - 1) / g.cols_per_warp;
+  return true;
 }
 
 extern "C" int ie_mlstm_chunks(int dk, int dv) {
-  if (dk <= 0 || dv <= 0 || mm_parts(dk) > 32) return 0;
-  const int cv = mm_chunk_cols(dk, dv);
-  return (dv + cv - 1) / cv;
+  MMGeometry g;
+  return mm_geometry(dk, dv, g) ? g.chunks : 0;
 }
 
 extern "C" long long ie_mlstm_state_floats(int dk, int dv) {
@@ -48,98 +61,159 @@ extern "C" long long ie_mlstm_state_floats(int dk, int dv) {
   return chunks ? (long long)dk * dv + (long long)chunks * (dk + 1) : 0;
 }
 
-template <typename TA, typename TW>
-__global__ void __launch_bounds__(MM_THREADS)
+// RPT > 0: every thread holds exactly RPT rows (dk = P * RPT, a multiple of 4): rows are read from shared memory in
+// 16-byte pieces and nothing is guarded.  RPT = 0: any sizes, row by row with guards.
+template <typename TA, typename TW, int RPT>
+__global__ void __launch_bounds__(MM_MAX_WARPS * 32)
 mlstm_scan_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, int q_stride, int k_stride,
                   int v_stride, const float* __restrict__ zi, const float* __restrict__ zf, int z_stride,
                   const TW* __restrict__ i_bias, const TW* __restrict__ f_bias, float cap, float q_scale,
                   float* __restrict__ state, long long state_stride, float* __restrict__ out, int out_stride,
-                  const int* __restrict__ q_start, const int* __restrict__ slots, int heads, int dk, int dv, int P, int CV,
+                  const int* __restrict__ q_start, const int* __restrict__ slots, int dk, int dv, MMGeometry geo, int tile,
                   int write_state) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   pdl_wait();
-  float* sq = sm;                         // [MM_TILE][dk]
-  float* sk = sq + MM_TILE * dk;          // [MM_TILE][dk]
-  float* sv = sk + MM_TILE * dk;          // [MM_TILE][CV]
-  float* sg = sv + MM_TILE * CV;          // [MM_TILE][2]: i, f
+  const int P = geo.P, RP = RPT > 0 ? RPT : geo.RP, CVB = geo.chunk_cols;
+  float* sq = sm;                         // [tile][dk]
+  float* sk = sq + tile * dk;             // [tile][dk]
+  float* sv = sk + tile * dk;             // [tile][CVB]
+  float* sg = sv + tile * CVB;            // [tile][2]: i, f; then a, b
+  float* se = sg + 2 * tile;              // [tile]: exp(-m)
+  float* s_m = se + tile;                 // [tile + 1]: m before the tile's first token, then after each token
   const int r_id = blockIdx.x, head = blockIdx.y, chunk = blockIdx.z;
   const int t0 = q_start[r_id], t1 = q_start[r_id + 1];
   const int slot = IE_SLOT(slots[r_id]);
   if (slot < 0 || t1 <= t0) return;
-  const int part = threadIdx.x % P, col_local = threadIdx.x / P;
-  const int col = chunk * CV + col_local;
-  const bool live = col_local < CV && col < dv;
-  const int n_chunks = (dv + CV - 1) / CV;
-  float* hs = state + (size_t)slot * state_stride + (size_t)head * ((size_t)dk * dv + (size_t)n_chunks * (dk + 1));
+  const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
+  const int part = lane % P, group = lane / P;
+  const bool is_n = group == geo.cols_per_warp;           // the warp's copy of the normaliser
+  const int v0 = chunk * CVB, v_cols = min(CVB, dv - v0);
+  const int col_local = warp * geo.cols_per_warp + group;
+  const bool live = !is_n && col_local < v_cols;
+  const int col = v0 + col_local;
+  const int n_lane = geo.cols_per_warp * P;               // where the warp's n . q ends up
+  float* hs = state + (size_t)slot * state_stride + (size_t)head * ((size_t)dk * dv + (size_t)geo.chunks * (dk + 1));
   float* hn = hs + (size_t)dk * dv + (size_t)chunk * (dk + 1);
-  float S[MM_ROWS], nn[MM_ROWS];
+  const int row0 = part * RP;
+  float S[MM_ROWS];
 #pragma unroll
   for (int i = 0; i < MM_ROWS; ++i) {
-    const int r = part + P * i;
-    S[i] = (live && r < dk) ? hs[(size_t)r * dv + col] : 0.f;
-    nn[i] = r < dk ? hn[r] : 0.f;
+    const int r = row0 + i;
+    const bool there = (RPT > 0 ? i < RPT : i < RP) && r < dk;
+    S[i] = !there ? 0.f : (is_n ? hn[r] : (live ? hs[(size_t)r * dv + col] : 0.f));
   }
-  float m = hn[dk];
+  if (tid == 0) s_m[0] = hn[dk];
   const float bi = to_f32(i_bias[head]), bf = to_f32(f_bias[head]);
-  for (int tile0 = t0; tile0 < t1; tile0 += MM_TILE) {
-    const int nt = min(MM_TILE, t1 - tile0);
+
+  // the next tile's inputs, on their way while this tile runs
+  TA rq[MM_FETCH], rk[MM_FETCH], rv[MM_FETCH];
+  float rzi = 0.f, rzf = 0.f;
+  auto fetch = [&](int tile0) {
+    const int nt = min(tile, t1 - tile0);
+#pragma unroll
+    for (int j = 0; j < MM_FETCH; ++j) {
+      const int idx = tid + j * nthr;
+      if (idx < nt * dk) {
+        const int tt = idx / dk, r = idx - tt * dk;
+        rq[j] = q[(size_t)(tile0 + tt) * q_stride + head * dk + r];
+        rk[j] = k[(size_t)(tile0 + tt) * k_stride + head * dk + r];
+      }
+      if (idx < nt * v_cols) {
+        const int tt = idx / v_cols, c = idx - tt * v_cols;
+        rv[j] = v[(size_t)(tile0 + tt) * v_stride + head * dv + v0 + c];
+      }
+    }
+    if (tid < nt) {
+      rzi = zi[(size_t)(tile0 + tid) * z_stride + head];
+      rzf = zf[(size_t)(tile0 + tid) * z_stride + head];
+    }
+  };
+  fetch(t0);
+  for (int tile0 = t0; tile0 < t1; tile0 += tile) {
+    const int nt = min(tile, t1 - tile0);
+    __syncthreads();                      // the tile before is used up
+#pragma unroll
+    for (int j = 0; j < MM_FETCH; ++j) {
+      const int idx = tid + j * nthr;
+      if (idx < nt * dk) {
+        sq[idx] = to_f32(rq[j]) * q_scale;
+        sk[idx] = to_f32(rk[j]);
+      }
+      if (idx < nt * v_cols) {
+        const int tt = idx / v_cols, c = idx - tt * v_cols;
+        sv[tt * CVB + c] = to_f32(rv[j]);
+      }
+    }
+    if (tid < nt) {
+      const float x = cap * tanhf((rzf + bf) / cap);
+      sg[2 * tid] = cap * tanhf((rzi + bi) / cap);
+      sg[2 * tid + 1] = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+    }
+    if (tile0 + tile < t1) fetch(tile0 + tile);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * dk; idx += blockDim.x) {
-      const int tt = idx / dk, r = idx - tt * dk;
-      sq[idx] = to_f32(q[(size_t)(tile0 + tt) * q_stride + head * dk + r]) * q_scale;
-      sk[idx] = to_f32(k[(size_t)(tile0 + tt) * k_stride + head * dk + r]);
+    if (tid == 0) {                       // the maxima, one after the other: additions and comparisons only
+      float m = s_m[0];
+      for (int tt = 0; tt < nt; ++tt) {
+        m = fmaxf(sg[2 * tt + 1] + m, sg[2 * tt]);
+        s_m[tt + 1] = m;
+      }
     }
-    for (int idx = threadIdx.x; idx < nt * CV; idx += blockDim.x) {
-      const int tt = idx / CV, c = idx - tt * CV;
-      sv[idx] = chunk * CV + c < dv ? to_f32(v[(size_t)(tile0 + tt) * v_stride + head * dv + chunk * CV + c]) : 0.f;
-    }
-    for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) {
-      const float ai = zi[(size_t)(tile0 + tt) * z_stride + head] + bi;
-      const float af = zf[(size_t)(tile0 + tt) * z_stride + head] + bf;
-      const float x = cap * tanhf(af / cap);
-      sg[2 * tt] = cap * tanhf(ai / cap);
-      sg[2 * tt + 1] = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+    __syncthreads();
+    if (tid < nt) {                       // the three exponentials of every token side by side
+      const float gi = sg[2 * tid], gf = sg[2 * tid + 1], m_old = s_m[tid], m_new = s_m[tid + 1];
+      sg[2 * tid] = expf(gf + m_old - m_new);
+      sg[2 * tid + 1] = expf(gi - m_new);
+      se[tid] = expf(-m_new);
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float gi = sg[2 * tt], gf = sg[2 * tt + 1];
-      const float m_new = fmaxf(gf + m, gi);
-      const float a = expf(gf + m - m_new), b = expf(gi - m_new);
-      m = m_new;
-      const float* qr = sq + tt * dk;
-      const float* kr = sk + tt * dk;
-      const float bv = b * sv[tt * CV + (col_local < CV ? col_local : 0)];
-      float acc = 0.f, nq = 0.f;
+      const float a = sg[2 * tt], b = sg[2 * tt + 1];
+      const float* qr = sq + tt * dk + row0;
+      const float* kr = sk + tt * dk + row0;
+      // what this column's value is: one for the normaliser, nothing for a column beyond the head
+      const float x = is_n ? b : (live ? b * sv[tt * CVB + col_local] : 0.f);
+      float acc0 = 0.f, acc1 = 0.f;
+      if (RPT > 0) {
 #pragma unroll
-      for (int i = 0; i < MM_ROWS; ++i) {
-        const int r = part + P * i;
-        if (r < dk) {
-          const float kv = kr[r], qv = qr[r];
-          S[i] = fmaf(a, S[i], kv * bv);
-          nn[i] = fmaf(a, nn[i], b * kv);
-          acc = fmaf(S[i], qv, acc);
-          nq = fmaf(nn[i], qv, nq);
+        for (int i = 0; i < RPT; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + i), q4 = *reinterpret_cast<const float4*>(qr + i);
+          S[i] = fmaf(a, S[i], k4.x * x);
+          S[i + 1] = fmaf(a, S[i + 1], k4.y * x);
+          S[i + 2] = fmaf(a, S[i + 2], k4.z * x);
+          S[i + 3] = fmaf(a, S[i + 3], k4.w * x);
+          acc0 = fmaf(S[i], q4.x, acc0);
+          acc1 = fmaf(S[i + 1], q4.y, acc1);
+          acc0 = fmaf(S[i + 2], q4.z, acc0);
+          acc1 = fmaf(S[i + 3], q4.w, acc1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < MM_ROWS; ++i) {
+          if (i < RP && row0 + i < dk) {
+            S[i] = fmaf(a, S[i], kr[i] * x);
+            if (i & 1) acc1 = fmaf(S[i], qr[i], acc1); else acc0 = fmaf(S[i], qr[i], acc0);
+          }
         }
       }
-      for (int o = 1; o < P; o <<= 1) {
-        acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        nq += __shfl_xor_sync(0xffffffffu, nq, o);
-      }
+      float acc = acc0 + acc1;
+      for (int o = 1; o < P; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      const float nq = __shfl_sync(0xffffffffu, acc, n_lane);
       if (live && part == 0)
-        out[(size_t)(tile0 + tt) * out_stride + head * dv + col] = acc / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+        out[(size_t)(tile0 + tt) * out_stride + head * dv + col] = acc / (fmaxf(fabsf(nq), se[tt]) + 1e-6f);
     }
+    if (tid == 0) s_m[0] = s_m[nt];       // (read again only after the next barrier)
   }
   if (!write_state) return;
 #pragma unroll
   for (int i = 0; i < MM_ROWS; ++i) {
-    const int r = part + P * i;
-    if (r < dk) {
+    const int r = row0 + i;
+    if ((RPT > 0 ? i < RPT : i < RP) && r < dk) {
       if (live) hs[(size_t)r * dv + col] = S[i];
-      if (col_local == 0) hn[r] = nn[i];
+      if (is_n && warp == 0) hn[r] = S[i];
     }
   }
-  if (threadIdx.x == 0) hn[dk] = m;
+  if (tid == 0) hn[dk] = s_m[0];
 }
 
 extern "C" int ie_mlstm_scan(const void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride,
@@ -148,26 +222,38 @@ extern "C" int ie_mlstm_scan(const void* q, const void* k, const void* v, int q_
                              int out_stride, const int* q_start, const int* slots, int n_requests, int heads, int dk,
                              int dv, int write_state, int act_dtype, cudaStream_t stream) {
   if (n_requests <= 0) return IE_OK;
-  if (heads <= 0 || heads > 65535 || dk <= 0 || dv <= 0 || !(cap > 0.f)) return IE_BAD_SIZE;
-  const int P = mm_parts(dk);
-  if (P > 32) return IE_BAD_SIZE;
-  const int CV = mm_chunk_cols(dk, dv);
-  const int chunks = (dv + CV - 1) / CV;
-  if (chunks > 65535) return IE_BAD_SIZE;
-  const size_t smem = sizeof(float) * ((size_t)2 * MM_TILE * dk + (size_t)MM_TILE * CV + 2 * MM_TILE);
+  if (heads <= 0 || heads > 65535 || !(cap > 0.f)) return IE_BAD_SIZE;
+  MMGeometry g;
+  if (!mm_geometry(dk, dv, g) || g.chunks > 65535) return IE_BAD_SIZE;
+  const int threads = g.warps * 32;
+  // tokens of a tile: what a thread can fetch ahead in MM_FETCH elements each of q, k and v
+  int tile = (MM_FETCH * threads) / (dk > g.chunk_cols ? dk : g.chunk_cols);
+  if (tile > MM_TILE) tile = MM_TILE;
+  if (tile > threads) tile = threads;
+  if (tile < 1) return IE_BAD_SIZE;
+  const size_t smem = sizeof(float) * ((size_t)2 * tile * dk + (size_t)tile * g.chunk_cols + 4 * tile + 1);
   if (smem > 48 * 1024) return IE_BAD_SIZE;
-  dim3 grid(n_requests, heads, chunks);
-  // whole warps, so that the shuffles of a column's threads always find their partners
-  const int threads = ((CV * P + 31) / 32) * 32;
-#define MM_GO(TA, TW)                                                                                              \
-  return launch_k(mlstm_scan_kernel<TA, TW>, grid, threads, smem, stream, (const TA*)q, (const TA*)k, (const TA*)v, \
-                  q_stride, k_stride, v_stride, zi, zf, z_stride, (const TW*)i_bias, (const TW*)f_bias, cap, q_scale, \
-                  state, state_stride, out, out_stride, q_start, slots, heads, dk, dv, P, CV, write_state)
+  dim3 grid(n_requests, heads, g.chunks);
+  // rows in 16-byte pieces when every thread holds the same multiple of four rows
+  const int rpt = (dk == g.P * g.RP && (g.RP & 3) == 0) ? g.RP : 0;
+#define MM_LAUNCH(TA, TW, R)                                                                                          \
+  return launch_k(mlstm_scan_kernel<TA, TW, R>, grid, threads, smem, stream, (const TA*)q, (const TA*)k, (const TA*)v, \
+                  q_stride, k_stride, v_stride, zi, zf, z_stride, (const TW*)i_bias, (const TW*)f_bias, cap, q_scale,  \
+                  state, state_stride, out, out_stride, q_start, slots, dk, dv, g, tile, write_state)
+#define MM_GO(TA, TW)               \
+  {                                 \
+    if (rpt == 16) MM_LAUNCH(TA, TW, 16); \
+    if (rpt == 12) MM_LAUNCH(TA, TW, 12); \
+    if (rpt == 8) MM_LAUNCH(TA, TW, 8);   \
+    if (rpt == 4) MM_LAUNCH(TA, TW, 4);   \
+    MM_LAUNCH(TA, TW, 0);           \
+  }
   if (act_dtype == IE_F32 && w_dtype == IE_F32) MM_GO(float, float);
   if (act_dtype == IE_F32 && w_dtype == IE_BF16) MM_GO(float, bf16);
   if (act_dtype == IE_BF16 && w_dtype == IE_F32) MM_GO(bf16, float);
   if (act_dtype == IE_BF16 && w_dtype == IE_BF16) MM_GO(bf16, bf16);
 #undef MM_GO
+#undef MM_LAUNCH
   return IE_BAD_DTYPE;
 }
 

@@ -117,9 +117,9 @@ def test_stream_kernels(dtype):
         row = torch.randn(d, generator=g).to(dt)
         k().add_row(xd, row.to(DEV))
         assert torch.allclose(xd.double().cpu(), want + row.double(), atol=3e-6)
-    for group, d in ((1, 30), (6, 30), (10, 40)):
-        buf = torch.randn(9, d + 5, generator=g).to(dt)
-        gate = torch.randn(9, d // group + 3, generator=g).to(dt)
+    for group, d, pad, gpad in ((1, 30, 5, 3), (6, 30, 5, 3), (10, 40, 5, 3), (1, 64, 8, 8), (16, 64, 8, 3)):   # the last two: 16-byte forms
+        buf = torch.randn(9, d + pad, generator=g).to(dt)
+        gate = torch.randn(9, d // group + gpad, generator=g).to(dt)
         bd = buf.to(DEV)
         k().gate_mul(bd[:, :d], gate.to(DEV)[:, :d // group], group=group)
         want = buf.double()[:, :d] * torch.sigmoid(gate.double()[:, :d // group]).repeat_interleave(group, dim=1)
@@ -127,13 +127,14 @@ def test_stream_kernels(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_token_shift_carries_the_last_row_over_any_cut(dtype):
+@pytest.mark.parametrize("d", [45, 64])                   # rows that take the 16-byte form in bfloat16, and rows that do not
+def test_token_shift_carries_the_last_row_over_any_cut(dtype, d):
     """Three requests of unequal length in slots out of order; whole, cut into portions (down to one token) and with a
     request left out of a step, the shifted rows are the same; a new request in a used slot starts from zeros when the
     slot was cleared."""
     dt = TORCH[dtype]
     g = torch.Generator().manual_seed(5)
-    d, lens, slots = 45, [13, 1, 6], [2, 0, 3]
+    lens, slots = [13, 1, 6], [2, 0, 3]
     mu = torch.rand(d, generator=g).to(dt)
     hs = [torch.randn(L, d, generator=g).to(dt) for L in lens]
     wants = [plain.token_shift(h.double(), mu.double()) for h in hs]
@@ -199,9 +200,9 @@ def test_qkv_prepare_kernel(dtype, heads, kv, hd, hdv, wide_row):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, kv, hdv, slice_heads, gated", [(4, 2, 24, 2, True), (6, 3, 8, 2, True), (5, 1, 6, 1, False),
-                                                               (3, 3, 10, 1, True)])
-def test_talk_combine_kernel(dtype, heads, kv, hdv, slice_heads, gated):
+@pytest.mark.parametrize("heads, kv, hdv, slice_heads, gated, pad", [(4, 2, 24, 2, True, 8), (6, 3, 8, 2, True, 2), (5, 1, 6, 1, False, 2),
+                                                                    (3, 3, 10, 1, True, 2), (8, 2, 16, 1, False, 8)])
+def test_talk_combine_kernel(dtype, heads, kv, hdv, slice_heads, gated, pad):
     """Every query head's weights applied to every value head, mixed into the heads' outputs, in slices of value heads."""
     dt = TORCH[dtype]
     g = torch.Generator().manual_seed(heads * 10 + kv)
@@ -209,7 +210,7 @@ def test_talk_combine_kernel(dtype, heads, kv, hdv, slice_heads, gated):
     a = torch.randn(n, heads, kv, hdv, generator=g).to(dt)
     talk = torch.randn(heads, heads, generator=g)
     gate = torch.randn(n, heads * hdv, generator=g).to(dt)
-    out = torch.zeros(n, heads * hdv + 2, dtype=dt, device=DEV)
+    out = torch.zeros(n, heads * hdv + pad, dtype=dt, device=DEV)      # a pad of 8 keeps rows on 16 bytes (the vector form)
     for c0 in range(0, kv, slice_heads):
         nc = min(slice_heads, kv - c0)
         part = a[:, :, c0:c0 + nc].reshape(n, heads * nc * hdv).to(DEV)
