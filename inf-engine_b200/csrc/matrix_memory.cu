@@ -29,7 +29,7 @@
 
 #define MM_ROWS 16
 #define MM_TILE 16
-#define MM_MAX_WARPS 16
+#define MM_MAX_WARPS 4
 #define MM_FETCH 12     // elements of a tile that a thread fetches ahead into registers, each of q, k and v
 
 struct MMGeometry {
@@ -106,23 +106,33 @@ mlstm_scan_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* 
   if (tid == 0) s_m[0] = hn[dk];
   const float bi = to_f32(i_bias[head]), bf = to_f32(f_bias[head]);
 
-  // the next tile's inputs, on their way while this tile runs
+  // the next tile's inputs, on their way while this tile runs; where each element of a tile lies is worked out once
   TA rq[MM_FETCH], rk[MM_FETCH], rv[MM_FETCH];
+  int at_q[MM_FETCH], at_k[MM_FETCH], at_v[MM_FETCH], to_v[MM_FETCH];
+#pragma unroll
+  for (int j = 0; j < MM_FETCH; ++j) {
+    const int idx = tid + j * nthr;
+    const int tt = idx / dk, r = idx - tt * dk;
+    at_q[j] = tt * q_stride + head * dk + r;
+    at_k[j] = tt * k_stride + head * dk + r;
+    const int tv = idx / v_cols, c = idx - tv * v_cols;
+    at_v[j] = tv * v_stride + head * dv + v0 + c;
+    to_v[j] = tv * CVB + c;
+  }
   float rzi = 0.f, rzf = 0.f;
   auto fetch = [&](int tile0) {
     const int nt = min(tile, t1 - tile0);
+    const TA* qt = q + (size_t)tile0 * q_stride;
+    const TA* kt = k + (size_t)tile0 * k_stride;
+    const TA* vt = v + (size_t)tile0 * v_stride;
 #pragma unroll
     for (int j = 0; j < MM_FETCH; ++j) {
       const int idx = tid + j * nthr;
       if (idx < nt * dk) {
-        const int tt = idx / dk, r = idx - tt * dk;
-        rq[j] = q[(size_t)(tile0 + tt) * q_stride + head * dk + r];
-        rk[j] = k[(size_t)(tile0 + tt) * k_stride + head * dk + r];
+        rq[j] = qt[at_q[j]];
+        rk[j] = kt[at_k[j]];
       }
-      if (idx < nt * v_cols) {
-        const int tt = idx / v_cols, c = idx - tt * v_cols;
-        rv[j] = v[(size_t)(tile0 + tt) * v_stride + head * dv + v0 + c];
-      }
+      if (idx < nt * v_cols) rv[j] = vt[at_v[j]];
     }
     if (tid < nt) {
       rzi = zi[(size_t)(tile0 + tid) * z_stride + head];
@@ -140,10 +150,7 @@ mlstm_scan_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* 
         sq[idx] = to_f32(rq[j]) * q_scale;
         sk[idx] = to_f32(rk[j]);
       }
-      if (idx < nt * v_cols) {
-        const int tt = idx / v_cols, c = idx - tt * v_cols;
-        sv[tt * CVB + c] = to_f32(rv[j]);
-      }
+      if (idx < nt * v_cols) sv[to_v[j]] = to_f32(rv[j]);
     }
     if (tid < nt) {
       const float x = cap * tanhf((rzf + bf) / cap);
@@ -167,27 +174,47 @@ mlstm_scan_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* 
       se[tid] = expf(-m_new);
     }
     __syncthreads();
+    // (vector form) the rows, the gates and the value of the token after are read while a token is worked on
+    constexpr int NV = RPT > 0 ? RPT / 4 : 1;
+    float4 k4[NV], q4[NV], k4n[NV], q4n[NV];
+    float a_n = 0.f, b_n = 0.f, v_n = 0.f, e_n = 0.f;
+    auto read_token = [&](int tt) {
+      a_n = sg[2 * tt];
+      b_n = sg[2 * tt + 1];
+      e_n = se[tt];
+      v_n = live ? sv[tt * CVB + col_local] : 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        k4n[i] = *reinterpret_cast<const float4*>(sk + tt * dk + row0 + 4 * i);
+        q4n[i] = *reinterpret_cast<const float4*>(sq + tt * dk + row0 + 4 * i);
+      }
+    };
+    if (RPT > 0) read_token(0);
     for (int tt = 0; tt < nt; ++tt) {
-      const float a = sg[2 * tt], b = sg[2 * tt + 1];
+      float a, b, x, e_here;
       const float* qr = sq + tt * dk + row0;
       const float* kr = sk + tt * dk + row0;
-      // what this column's value is: one for the normaliser, nothing for a column beyond the head
-      const float x = is_n ? b : (live ? b * sv[tt * CVB + col_local] : 0.f);
       float acc0 = 0.f, acc1 = 0.f;
       if (RPT > 0) {
+        a = a_n; b = b_n; e_here = e_n;
+        x = is_n ? b : b * v_n;            // one for the normaliser's column, nothing for a column beyond the head
 #pragma unroll
-        for (int i = 0; i < RPT; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(kr + i), q4 = *reinterpret_cast<const float4*>(qr + i);
-          S[i] = fmaf(a, S[i], k4.x * x);
-          S[i + 1] = fmaf(a, S[i + 1], k4.y * x);
-          S[i + 2] = fmaf(a, S[i + 2], k4.z * x);
-          S[i + 3] = fmaf(a, S[i + 3], k4.w * x);
-          acc0 = fmaf(S[i], q4.x, acc0);
-          acc1 = fmaf(S[i + 1], q4.y, acc1);
-          acc0 = fmaf(S[i + 2], q4.z, acc0);
-          acc1 = fmaf(S[i + 3], q4.w, acc1);
+        for (int i = 0; i < NV; ++i) { k4[i] = k4n[i]; q4[i] = q4n[i]; }
+        if (tt + 1 < nt) read_token(tt + 1);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          S[4 * i] = fmaf(a, S[4 * i], k4[i].x * x);
+          S[4 * i + 1] = fmaf(a, S[4 * i + 1], k4[i].y * x);
+          S[4 * i + 2] = fmaf(a, S[4 * i + 2], k4[i].z * x);
+          S[4 * i + 3] = fmaf(a, S[4 * i + 3], k4[i].w * x);
+          acc0 = fmaf(S[4 * i], q4[i].x, acc0);
+          acc1 = fmaf(S[4 * i + 1], q4[i].y, acc1);
+          acc0 = fmaf(S[4 * i + 2], q4[i].z, acc0);
+          acc1 = fmaf(S[4 * i + 3], q4[i].w, acc1);
         }
       } else {
+        a = sg[2 * tt]; b = sg[2 * tt + 1]; e_here = se[tt];
+        x = is_n ? b : (live ? b * sv[tt * CVB + col_local] : 0.f);
 #pragma unroll
         for (int i = 0; i < MM_ROWS; ++i) {
           if (i < RP && row0 + i < dk) {
@@ -200,7 +227,7 @@ mlstm_scan_kernel(const TA* __restrict__ q, const TA* __restrict__ k, const TA* 
       for (int o = 1; o < P; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       const float nq = __shfl_sync(0xffffffffu, acc, n_lane);
       if (live && part == 0)
-        out[(size_t)(tile0 + tt) * out_stride + head * dv + col] = acc / (fmaxf(fabsf(nq), se[tt]) + 1e-6f);
+        out[(size_t)(tile0 + tt) * out_stride + head * dv + col] = acc / (fmaxf(fabsf(nq), e_here) + 1e-6f);
     }
     if (tid == 0) s_m[0] = s_m[nt];       // (read again only after the next barrier)
   }
