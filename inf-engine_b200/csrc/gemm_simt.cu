@@ -128,7 +128,8 @@ __global__ void __launch_bounds__(256) gemm_rowdot_kernel(const TA* __restrict__
   for (int k = threadIdx.x; k < K; k += blockDim.x) a_s[k] = to_f32(A[(size_t)m * lda + k]);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int n = warp; n < N; n += 8) {
+  // blocks along y share a row's outputs in groups of eight (a few rows then still fill the device)
+  for (int n = blockIdx.y * 8 + warp; n < N; n += 8 * gridDim.y) {
     const TW* w = W + (size_t)n * ldw;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int k = lane;
@@ -147,6 +148,8 @@ extern "C" int ie_gemm_rowdot(const void* A, int a_dtype, const void* W, int w_d
   if (M <= 0 || N <= 0) return IE_OK;
   if (K <= 0 || (size_t)K * sizeof(float) > 200 * 1024) return IE_BAD_SIZE;
   const size_t smem = (size_t)K * sizeof(float);
+  // few rows (decode tokens): a block a row and eight outputs, so that the weight rows stream through many blocks
+  const dim3 grid(M, M <= 128 ? (N + 7) / 8 : 1);
 #define RD_GO(TA, TW)                                                                                              \
   {                                                                                                                \
     if (smem > 47 * 1024) {                                                                                        \
@@ -154,7 +157,7 @@ extern "C" int ie_gemm_rowdot(const void* A, int a_dtype, const void* W, int w_d
                                            (int)smem);                                                             \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    return launch_k(gemm_rowdot_kernel<TA, TW>, M, 256, smem, stream, (const TA*)A, (const TW*)W, C, N, K, lda, ldw, \
+    return launch_k(gemm_rowdot_kernel<TA, TW>, grid, 256, smem, stream, (const TA*)A, (const TW*)W, C, N, K, lda, ldw, \
                     ldc);                                                                                          \
   }
   if (a_dtype == IE_F32 && w_dtype == IE_F32) RD_GO(float, float);

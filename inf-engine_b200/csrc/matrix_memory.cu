@@ -296,6 +296,25 @@ __global__ void mlstm_finish_kernel(const float* __restrict__ o, int o_stride, c
   if (w >= (long long)n * heads) return;
   const int t = (int)(w / heads), h = (int)(w - (long long)t * heads);
   const float* row = o + (size_t)t * o_stride + h * dv;
+  if (sizeof(TA) == 2 && sizeof(TW) == 2 && (dv & 63) == 0 && ((o_stride | gate_stride | out_stride) & 1) == 0) {
+    // pairs of neighbouring coordinates: 8-byte loads of o, 4-byte ones of gain, gate and result
+    float ss = 0.f;
+    for (int d = 2 * lane; d < dv; d += 64) {
+      const float2 v = *reinterpret_cast<const float2*>(row + d);
+      ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss));
+    }
+    ss = warp_sum(ss);
+    const float r = sqrtf(ss / (float)dv + eps);
+    for (int d = 2 * lane; d < dv; d += 64) {
+      const int c = h * dv + d;
+      const float2 v = *reinterpret_cast<const float2*>(row + d);
+      const float2 gn = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gain + c));
+      const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)t * gate_stride + c));
+      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * out_stride + c) =
+          __floats2bfloat162_rn(v.x / r * gn.x / (1.f + expf(-z.x)), v.y / r * gn.y / (1.f + expf(-z.y)));
+    }
+    return;
+  }
   float ss = 0.f;
   for (int d = lane; d < dv; d += 32) ss = fmaf(row[d], row[d], ss);
   ss = warp_sum(ss);

@@ -14,26 +14,33 @@
 //   size); sigmoid and product in float32.
 #include "common.cuh"
 
+// A thread keeps one coordinate and walks SIN_TOKENS tokens: its frequency (a double-precision exponential) is formed once.
+#define SIN_TOKENS 16
 __global__ void scale_add_sinusoid_kernel(float* __restrict__ x, const int* __restrict__ positions, float scale,
                                           double log_base, int n, int d) {
   pdl_trigger();
   pdl_wait();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)n * d) return;
-  const int t = (int)(i / d), c = (int)(i - (long long)t * d);
-  const double turns = (double)positions[t] * exp(-log_base * (double)(c & ~1) / (double)d) * 0.15915494309189535;
-  float sn, cs;
-  sincosf((float)((turns - floor(turns)) * 6.283185307179586), &sn, &cs);
-  x[i] = fmaf(x[i], scale, (c & 1) ? cs : sn);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  const double turns_per_position = exp(-log_base * (double)(c & ~1) / (double)d) * 0.15915494309189535;
+  const int t_end = min(n, ((int)blockIdx.y + 1) * SIN_TOKENS);
+  for (int t = blockIdx.y * SIN_TOKENS; t < t_end; ++t) {
+    const double turns = (double)positions[t] * turns_per_position;
+    float sn, cs;
+    sincosf((float)((turns - floor(turns)) * 6.283185307179586), &sn, &cs);
+    float* at = x + (size_t)t * d + c;
+    *at = fmaf(*at, scale, (c & 1) ? cs : sn);
+  }
 }
 
 extern "C" int ie_scale_add_sinusoid(float* x, const int* positions, float scale, double base, int n, int d,
                                      cudaStream_t stream) {
   if (n <= 0 || d <= 0) return IE_OK;
   if (!(base > 0.0)) return IE_BAD_SIZE;
-  const long long total = (long long)n * d;
-  return launch_k(scale_add_sinusoid_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, positions, scale,
-                  log(base), n, d);
+  const int threads = d >= 256 ? 256 : ((d + 31) / 32) * 32;
+  const dim3 grid((d + threads - 1) / threads, (n + SIN_TOKENS - 1) / SIN_TOKENS);
+  if (grid.y > 65535) return IE_BAD_SIZE;
+  return launch_k(scale_add_sinusoid_kernel, grid, threads, 0, stream, x, positions, scale, log(base), n, d);
 }
 
 template <typename TW>
