@@ -453,7 +453,8 @@ def _gavatar_configs(size):
     mlp = {"kind": "moe", "expert": {"ff": inter // 4}, "router": {"experts": 16, "top": 4}}
     mem = {"type": "mlstm", "mixer": {"heads": H, "dim": FAMILY_HD, "vdim": FAMILY_HD, "gate_cap": 15.0}, "mlp": mlp}
     att = {"type": "attention", "mlp": mlp,
-           "mixer": {"heads": H, "kv_heads": G, "dim": FAMILY_HD, "vdim": FAMILY_HD, "scale": 8.0, "mask": {"size": GAVATAR_WINDOW}}}
+           "mixer": {"heads": H, "kv_heads": G, "dim": FAMILY_HD, "vdim": FAMILY_HD, "scale": FAMILY_HD ** -0.5,
+                     "mask": {"size": GAVATAR_WINDOW}}}
     lat = {"type": "latent_attention", "mlp": mlp,
            "mixer": {"heads": H, "dim": FAMILY_HD, "vdim": FAMILY_HD, "q_rank": w // 2, "kv_rank": GAVATAR_RANK,
                      "scale": FAMILY_HD ** -0.5, "mask": {"size": GAVATAR_WINDOW}}}

@@ -564,6 +564,24 @@ def test_edges_of_the_windows_in_prompts_and_in_decoding(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("windows", [(1, 2), (2, 1), (500, 8)])
+def test_the_shortest_windows_and_one_longer_than_the_sequence(tmp_path, dtype, windows):
+    """A window of one key (a token sees itself alone), of two, and one that no sequence of the test fills, on either
+    kind of attention, in a prompt, decoded and in portions of two."""
+    from gavatar_models import _att, _lat, _model, _moe
+    config = _model(90, 48, 1e-5, 1.5, [_att(4, 2, 12, 8, 0.5, windows[0], None), _lat(2, 12, 8, 10, 16, 0.5, windows[1], _moe(3, 1, 20))])
+    folder = make_gavatar_dir(tmp_path, "windows", config=config, fix=routers_for(dtype))
+    cfg, w = plain_inputs(folder)
+    toks = steady_tokens(cfg, w, 45, 5)
+    ref = reference(w, cfg, toks, dtype)
+    r = load(folder, dtype, page_size=8)
+    assert_close(stepped(r, "whole", toks, [45]), ref, dtype, f"windows {windows}: whole")
+    assert_close(stepped(r, "decode", toks, [5] + [1] * 40), ref, dtype, f"windows {windows}: decoded")
+    assert_close(stepped(r, "pairs", toks, [2]), ref, dtype, f"windows {windows}: portions of two")
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_a_far_key_is_found_by_the_latent_attention(tmp_path, dtype):
     """A latent attention without a window, made sharp; the test first shows that swapping one token 250 and more
     positions back moves the last positions' plain logits, then the engine must agree with the plain model there, in a
