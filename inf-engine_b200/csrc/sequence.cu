@@ -91,6 +91,70 @@ extern "C" int ie_outnorm_accumulate(float* residual, const void* y, int y_dtype
   return IE_BAD_DTYPE;
 }
 
+// The same, followed by the norm that the residual meets next: normed[row] = x / sqrt(mean(x^2) + eps2) * gain2 with x
+// the new residual row (kept in shared memory between the two sums), in the activation type.
+template <typename TY, typename TW, typename TW2, typename TA>
+__global__ void outnorm_accumulate_norm_kernel(float* __restrict__ residual, const TY* __restrict__ y, int y_stride,
+                                               const TW* __restrict__ gain, float eps, const TW2* __restrict__ gain2,
+                                               float eps2, TA* __restrict__ normed, int d) {
+  extern __shared__ float ys[];
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const TY* yr = y + (size_t)row * y_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = to_f32(yr[i]);
+    ys[i] = v;
+    ss += v * v;
+  }
+  const float rms = sqrtf(block_sum(ss, red) / (float)d + eps);
+  float* res = residual + (size_t)row * d;
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float x = res[i] + (ys[i] / rms) * to_f32(gain[i]);
+    res[i] = x;
+    ys[i] = x;
+    ss2 += x * x;
+  }
+  const float rms2 = sqrtf(block_sum(ss2, red) / (float)d + eps2);
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    normed[(size_t)row * d + i] = from_f32<TA>(ys[i] / rms2 * to_f32(gain2[i]));
+}
+
+extern "C" int ie_outnorm_accumulate_norm(float* residual, const void* y, int y_dtype, int y_stride, const void* gain,
+                                          int gain_dtype, float eps, const void* gain2, int gain2_dtype, float eps2,
+                                          void* normed, int normed_dtype, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows <= 0) return IE_OK;
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 200 * 1024) return IE_BAD_SIZE;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define ON_GO(TY, TW, TW2, TA)                                                                                          \
+  {                                                                                                                     \
+    if (smem > 47 * 1024) {                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(outnorm_accumulate_norm_kernel<TY, TW, TW2, TA>,                             \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
+      if (e != cudaSuccess) return (int)e;                                                                              \
+    }                                                                                                                   \
+    return launch_k(outnorm_accumulate_norm_kernel<TY, TW, TW2, TA>, n_rows, threads, smem, stream, residual,           \
+                    (const TY*)y, y_stride, (const TW*)gain, eps, (const TW2*)gain2, eps2, (TA*)normed, d);              \
+  }
+#define ON_GAINS(TY, TA)                                                          \
+  {                                                                               \
+    if (gain_dtype == IE_F32 && gain2_dtype == IE_F32) ON_GO(TY, float, float, TA); \
+    if (gain_dtype == IE_BF16 && gain2_dtype == IE_BF16) ON_GO(TY, bf16, bf16, TA); \
+    return IE_BAD_DTYPE;                                                          \
+  }
+  if (y_dtype == IE_F32 && normed_dtype == IE_F32) ON_GAINS(float, float);
+  if (y_dtype == IE_F32 && normed_dtype == IE_BF16) ON_GAINS(float, bf16);
+  if (y_dtype == IE_BF16 && normed_dtype == IE_BF16) ON_GAINS(bf16, bf16);
+  if (y_dtype == IE_BF16 && normed_dtype == IE_F32) ON_GAINS(bf16, float);
+#undef ON_GAINS
+#undef ON_GO
+  return IE_BAD_DTYPE;
+}
+
 // ------------------------------------------------------------------ short causal convolution with state
 // out[t, c] = act(bias[c] + sum_j w[c, j] * x[t - (taps - 1 - j), c]): the last column of w multiplies the current
 // token's input.  Inputs before the first token of the step come from the request's state, [taps - 1, channels] in

@@ -92,6 +92,8 @@ def core():
         lib.ie_gemm_rowdot.argtypes = [P, I, P, I, P, I, I, I, I, I, I, P]
         lib.ie_cast_rows.argtypes = [P, P, I, I, I, P]
         lib.ie_outnorm_accumulate.argtypes = [P, P, I, I, P, I, P, I, I, I, F, P]
+        lib.ie_outnorm_accumulate_norm.argtypes = [P, P, I, I, P, I, F, P, I, F, P, I, I, I, P]
+        lib.ie_outnorm_accumulate_norm.restype = c_int
         lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, I, P]
         lib.ie_attention_rows.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, I, I, I, P, P]
         lib.ie_linear_recurrence.argtypes = [P, I, P, I, P, P, I, P, P, P, I, P, P, I, P, P, I, I, F, F, I, I, P]
@@ -396,6 +398,20 @@ def outnorm_accumulate(residual: torch.Tensor, y: torch.Tensor, gain: torch.Tens
                                         dtype_code(gain.dtype), _ptr(next_in),
                                         dtype_code(next_in.dtype) if next_in is not None else IE_BF16, n, d, float(eps),
                                         _stream()), "outnorm_accumulate")
+
+
+def outnorm_accumulate_norm(residual: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float,
+                            next_gain: torch.Tensor, next_eps: float, normed: torch.Tensor) -> None:
+    """``outnorm_accumulate`` and, in the same kernel, the norm that the residual meets next:
+    ``normed = x / sqrt(mean(x^2) + next_eps) * next_gain`` with x the new residual rows, in ``normed``'s type."""
+    n, d = residual.shape
+    assert residual.dtype is torch.float32 and residual.is_contiguous() and y.shape == (n, d) and y.stride(1) == 1
+    assert gain.shape == (d,) and next_gain.shape == (d,) and gain.dtype == next_gain.dtype
+    assert normed.is_contiguous() and normed.shape == (n, d)
+    _check(core().ie_outnorm_accumulate_norm(_ptr(residual), _ptr(y), dtype_code(y.dtype), y.stride(0), _ptr(gain),
+                                             dtype_code(gain.dtype), float(eps), _ptr(next_gain), dtype_code(next_gain.dtype),
+                                             float(next_eps), _ptr(normed), dtype_code(normed.dtype), n, d, _stream()),
+           "outnorm_accumulate_norm")
 
 
 CONV_MAX_TAPS = 16

@@ -213,7 +213,8 @@ class SandwichBlock:
     each sublayer.  ``shift`` (optional) replaces what the mixer reads, h, by ``h + (h' - h) * mu`` with h' the h of the
     token before and mu a learned vector; the last h of every request is state of the run, kept beside the mixer's own
     cache (the run's requirement is then the pair, the mixer's first).  The residual is float32; the norm after a
-    sublayer and the sum into the residual are one kernel."""
+    sublayer and the sum into the residual are one kernel, which after the mixer also forms the feed-forward's normed
+    input."""
 
     @staticmethod
     def expected_tensors(spec):
@@ -271,10 +272,17 @@ class SandwichBlock:
             kernels.token_shift(h, shifted, self.shift, last.state, ctx.q_start, ctx.ctx_before, ctx.slots,
                                 ctx.n_requests, write_state=cache.write)
             h = shifted
-        self.mixer_out_norm.accumulate(residual, self.mixer.forward(h, ctx, mixer_cache))
-        if self.feedforward is not None:
+        y = self.mixer.forward(h, ctx, mixer_cache)
+        if self.feedforward is None:
+            self.mixer_out_norm.accumulate(residual, y)
+            return residual, None
+        # the norm after the mixer, the sum into the residual and the norm before the feed-forward: one kernel
+        fused = getattr(self.mixer_out_norm, "accumulate_then_norm", None)
+        h = fused(residual, y, self.ff_norm) if fused is not None else None
+        if h is None:
+            self.mixer_out_norm.accumulate(residual, y)
             h = self.ff_norm.add_norm(residual, None)
-            self.ff_out_norm.accumulate(residual, self.feedforward.forward(h, ctx))
+        self.ff_out_norm.accumulate(residual, self.feedforward.forward(h, ctx))
         return residual, None
 
 

@@ -40,6 +40,15 @@ class RMSNorm:
         """residual += norm(y); ``next_in`` (activation type, optional) takes the new residual rows."""
         kernels.outnorm_accumulate(residual, y, self.gain, self.eps, next_in)
 
+    def accumulate_then_norm(self, residual: torch.Tensor, y: torch.Tensor, next_norm, out_name: str = "normed"):
+        """residual += norm(y), and in the same kernel the rows that ``next_norm`` (an RMS norm of this size) makes of
+        the new residual; None when the two do not go together (the caller then runs them one after the other)."""
+        if not isinstance(next_norm, RMSNorm) or next_norm.size != self.size or next_norm.gain.dtype != self.gain.dtype:
+            return None
+        out = self.rt.ws.take(out_name, tuple(residual.shape), self.rt.act_dtype)
+        kernels.outnorm_accumulate_norm(residual, y, self.gain, self.eps, next_norm.gain, next_norm.eps, out)
+        return out
+
     def fusable_rms(self):
         """(gain, eps) for kernels that apply this norm inside a matrix product's prologue."""
         return self.gain, self.eps

@@ -127,6 +127,21 @@ def test_stream_kernels(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_into_the_residual_with_the_norm_that_follows(dtype):
+    """residual += norm(y) * gain and, in the same kernel, the next norm of the new residual."""
+    dt = TORCH[dtype]
+    g = torch.Generator().manual_seed(9)
+    for n, d in ((5, 37), (9, 192), (3, 2048)):
+        res, y = torch.randn(n, d, generator=g), (torch.randn(n, d + 3, generator=g) * 2).to(dt)
+        g1, g2 = 1 + 0.3 * torch.randn(d, generator=g), 1 + 0.3 * torch.randn(d, generator=g)
+        rd, out = res.to(DEV), torch.empty(n, d, dtype=dt, device=DEV)
+        k().outnorm_accumulate_norm(rd, y.to(DEV)[:, :d], g1.to(DEV), 1e-5, g2.to(DEV), 1e-6, out)
+        want_res = res.double() + plain.rms(y.double()[:, :d], 1e-5) * g1.double()
+        assert torch.allclose(rd.double().cpu(), want_res, atol=2e-5, rtol=2e-5)
+        assert close(out, plain.rms(want_res, 1e-6) * g2.double(), dtype, rel=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d", [45, 64])                   # rows that take the 16-byte form in bfloat16, and rows that do not
 def test_token_shift_carries_the_last_row_over_any_cut(dtype, d):
     """Three requests of unequal length in slots out of order; whole, cut into portions (down to one token) and with a
