@@ -166,8 +166,8 @@ class LatentAttentionSpec(MixerSpec):
     q_down: str = ""
     q_norm: str = ""
     window: int | None = None      # a query sees itself and the window - 1 keys before it (None: every earlier key)
-    sink: str | None = None        # tensor [n_heads]: exp(sink_h) joins the softmax's denominator of head h; it has no
-                                   # key and no value and is not scaled
+    sink: str | None = None        # tensor [n_heads]: exp(sink_h) joins the softmax's denominator of head h: a learned
+                                   # logit beside the keys' scores that ``scale`` does not multiply and that weighs nothing
     head_gate: str | None = None   # tensor [n_heads, hidden]: head h's output is multiplied by sigmoid(head_gate x)_h
 
 
@@ -480,7 +480,7 @@ class BlockSpec:
     ff_gate: str | None = None
     ff_gate_bias: str | None = None
     # "sandwich": x += out_norm(part(norm(x))): a norm before and after each sublayer (``mixer_norm`` / ``ff_norm``
-    # before, these two after).  ``token_shift`` names a tensor [hidden]: what the mixer reads, h = mixer_norm(x), is
+    # before, these two after).  ``token_shift`` names a tensor [hidden]: the mixer's input, h = mixer_norm(x), is
     # replaced by h + (h' - h) * token_shift with h' the h of the token before (zeros before the first); the last h of a
     # sequence is state of the run beside the mixer's own.
     mixer_out_norm: NormSpec | None = None

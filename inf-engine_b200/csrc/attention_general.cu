@@ -59,8 +59,8 @@ struct AttnGeneralParams {
   int n_v_heads;            // value heads in the value pool; kv head c reads value head c / (n_kv_heads / n_v_heads)
   int v_row;                // elements between two value rows of the value pool (the value size, or a key row's size
                             // when the values are the first dimensions of the keys and both pools are one)
-  const float* sink;        // [n_heads] or null: the softmax's denominator also holds exp(sink[head]), a term that has
-                            // no key and no value and is not scaled
+  const float* sink;        // [n_heads] or null: the softmax's denominator also holds exp(sink[head]): a learned
+                            // logit beside the keys' scores that `scale` does not multiply and that weighs nothing
 };
 
 // the normaliser of a row whose visible keys gave the sum l at the maximum m, with the sink's term added

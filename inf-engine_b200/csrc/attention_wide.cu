@@ -56,7 +56,7 @@ struct WideParams {
   // n_splits > 1: block z takes the keys [first + z * split_keys, first + (z + 1) * split_keys) of its tile's range
   // (split_keys a multiple of the key tile) and leaves sums, maxima and unnormalised outputs for the merge kernel
   int n_splits, split_keys;
-  const float* sink;  // [n_heads] or null: the denominator of head h also holds exp(sink[h]) (no key, no value, not scaled)
+  const float* sink;  // [n_heads] or null: the denominator of head h also holds exp(sink[h]), a logit that weighs nothing
   float* part_o;   // [blocks x, key heads, splits, BM, DV]
   float* part_ml;  // [blocks x, key heads, splits, BM, 2]
 };

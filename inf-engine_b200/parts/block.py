@@ -210,7 +210,7 @@ class GatedPreNormBlock:
 @register_block("sandwich")
 class SandwichBlock:
     """``x += out_norm1(mixer(shift(norm1(x))))``, then ``x += out_norm2(ff(norm2(x)))``: a norm before and a norm after
-    each sublayer.  ``shift`` (optional) replaces what the mixer reads, h, by ``h + (h' - h) * mu`` with h' the h of the
+    each sublayer.  ``shift`` (optional) replaces the mixer's input h by ``h + (h' - h) * mu`` with h' the h of the
     token before and mu a learned vector; the last h of every request is state of the run, kept beside the mixer's own
     cache (the run's requirement is then the pair, the mixer's first).  The residual is float32; the norm after a
     sublayer and the sum into the residual are one kernel, which after the mixer also forms the feed-forward's normed
